@@ -35,8 +35,8 @@ def uniform_from_state(seed_lo, seed_hi, draws):
 class PlainOps:
     name = "plain"
 
-    def embed(self, token_ids, table, out):
-        out.copy_(table[token_ids.long()].float())
+    def embed(self, token_ids, table, out, scale=1.0):
+        out.copy_(table[token_ids.long()].float() * scale)
 
     def add_rmsnorm(self, resid, delta, weight, eps, out):
         if delta is not None:
@@ -97,7 +97,7 @@ class PlainOps:
             v_pages[page, :, off, :] = v
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
-                        query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out, softcap=0.0):
+                        query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out, softcap=0.0, chunk=0):
         D, G = head_dim, num_heads // num_kv_heads
         qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
         for i in range(num_seqs):
@@ -115,6 +115,8 @@ class PlainOps:
             vis = kpos <= qpos
             if window:
                 vis = vis & (kpos > qpos - window)
+            if chunk:
+                vis = vis & (kpos // chunk == qpos // chunk)
             for h in range(num_heads):
                 s = (q[:, h] @ k[:, h // G].T) * scale
                 if softcap:

@@ -5,10 +5,10 @@ The reference keeps one pool ``kv[L, 2, pages, page, Hkv, D]`` with one allocato
 Python block table per ``Sequence`` (serving/kv_pool.py:12-21, serving/sequence.py:14-30).
 Here the cache needs of a model's run entries (an entry may have several: a block
 reports one per cache-using sub-part) are sorted into **groups** by what they ask for
-(kv heads, head size, window, page size): a group has its own page size, its own number
-of pages, its own allocator and its own block table per request, so a windowed layer
-can give pages back - and needs far fewer pages to begin with - while a full-attention
-layer keeps all of its.  A page id addresses the same slab in every cache layer of its
+(kv heads, head size, window or chunk, page size): a group has its own page size, its own number
+of pages, its own allocator and its own block table per request, so a windowed layer (or one
+whose tokens read only the keys of their own chunk of positions) can give pages back - and
+needs far fewer pages to begin with - while a full-attention layer keeps all of its.  A page id addresses the same slab in every cache layer of its
 group and in K and V, as in the reference.
 
 Sizing.  With an explicit ``num_pages`` every group gets room for the same number of
@@ -19,9 +19,9 @@ windowed group never needs more than ``max_slots`` requests x (window + longest
 step) tokens: its share stops growing there and the rest goes to the other groups.
 
 Pages go back to the allocator when the request is released (finished or preempted)
-and, for a windowed group, as soon as every position of the page lies before the
-window of the next token to run; a freed page's table entry becomes 0 (scratch) and is
-never read because the kernels start at the window's first key.  Freed pages are used
+and, for a windowed or chunked group, as soon as every position of the page lies before the
+window (or the chunk) of the next token to run; a freed page's table entry becomes 0 (scratch) and is
+never read because the kernels start at the window's (the chunk's) first key.  Freed pages are used
 again at once (LIFO) and are not cleared: reads are bounded by the request's length.
 
 State slots: ``max_slots`` ids; a request takes one at admission and gives it back at
@@ -66,8 +66,16 @@ class CacheGroup:
     def window(self):
         return self.need.window
 
+    @property
+    def reach(self):
+        """The most keys behind (and including) its own that a token of this group reads: the window, the chunk size,
+        or None for all of them."""
+        return self.need.window if self.need.window is not None else self.need.chunk
+
     def first_needed_page(self, start: int) -> int:
         """First logical page a token at position >= start can still read."""
+        if self.need.chunk is not None:
+            return (start - start % self.need.chunk) // self.page_size
         if self.window is None:
             return 0
         first_key = max(0, start - self.window + 1)
@@ -81,9 +89,9 @@ class CacheGroup:
         """The most pages a request of ``num_tokens`` holds at one time: all of them, or - with a window - those
         of the window plus the longest step (pages the window has passed are given back before new ones are taken)."""
         whole = pages_for(num_tokens, self.page_size)
-        if self.window is None or max_step_tokens is None:
+        if self.reach is None or max_step_tokens is None:
             return whole
-        return min(whole, pages_for(self.window + max_step_tokens - 1, self.page_size) + 1)
+        return min(whole, pages_for(self.reach + max_step_tokens - 1, self.page_size) + 1)
 
 
 class CacheManager:
@@ -144,7 +152,7 @@ class CacheManager:
         """Pages per group (scratch page included) for the largest token capacity that fits ``budget`` bytes."""
         def pages(g: CacheGroup, tokens: int) -> int:
             n = pages_for(tokens, g.page_size)
-            if g.window is not None and self.max_step_tokens is not None:
+            if g.reach is not None and self.max_step_tokens is not None:
                 n = min(n, self.max_slots * g.pages_of_request(tokens, self.max_step_tokens))
             return n + 1
 
@@ -183,7 +191,7 @@ class CacheManager:
         for g in self.groups:
             table = g.tables[rid]
             last = pages_for(new_len, g.page_size)
-            if g.window is None:                               # nothing is ever given back early: only growth
+            if g.reach is None:                                # nothing is ever given back early: only growth
                 plan.append(([], list(range(len(table), last)), last))
                 continue
             first = g.first_needed_page(start)

@@ -29,7 +29,7 @@ struct MmaParams {
     const int* qsl; const int* seq_lens;
     __nv_bfloat16* out;
     int num_seqs, Hq, Hkv;
-    float scale_log2; int window;
+    float scale_log2; int window, chunk;
     float cap_in, cap_out;              // score softcap: raw score s becomes cap_out * tanh(s * cap_in) (cap_in 0: none)
     int row_tiles, num_splits, split_len;
     float* ws_o; float* ws_ml;
@@ -102,7 +102,7 @@ paged_attn_mma_kernel(const MmaParams p) {
 
     const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
     int k_hi = ctx + tok_hi + 1;
-    int k_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int k_lo = first_visible_key(ctx + tok_lo, p.window, p.chunk);
     if (p.num_splits > 1) {
         const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
         k_lo = max(k_lo, split * piece);
@@ -118,14 +118,14 @@ paged_attn_mma_kernel(const MmaParams p) {
         rrow[h] = row;
         rvalid[h] = row < nrows;
         rpos[h] = rvalid[h] ? ctx + row / G : -1;
-        rlo[h] = p.window > 0 ? max(0, rpos[h] - p.window + 1) : 0;
+        rlo[h] = first_visible_key(rpos[h], p.window, p.chunk);
     }
     // position range of the warp's rows (uniform over the warp)
     const int wrow_lo = row0 + warp * 16, wrow_hi = min(nrows, wrow_lo + 16) - 1;
     const bool warp_active = wrow_lo < nrows;
     const int wpos_hi = warp_active ? ctx + wrow_hi / G : -1;
     const int wpos_lo = warp_active ? ctx + wrow_lo / G : -1;
-    const int wkey_lo = p.window > 0 ? max(0, wpos_lo - p.window + 1) : 0;
+    const int wkey_lo = first_visible_key(wpos_lo, p.window, p.chunk);
 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[D / 8][4];
@@ -219,7 +219,7 @@ paged_attn_mma_kernel(const MmaParams p) {
                 }
             }
             // scale, mask, running maximum
-            const bool full = kt + BN - 1 <= wpos_lo && kt >= (p.window > 0 ? max(0, wpos_hi - p.window + 1) : 0) && kt + BN <= k_hi
+            const bool full = kt + BN - 1 <= wpos_lo && kt >= (first_visible_key(wpos_hi, p.window, p.chunk)) && kt + BN <= k_hi
                               && wrow_hi - wrow_lo == 15;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -390,7 +390,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
 
     const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
     int k_hi = ctx + tok_hi + 1;
-    int k_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int k_lo = first_visible_key(ctx + tok_lo, p.window, p.chunk);
     k_lo = max(k_lo, (int)rank * p.split_len);
     k_hi = min(k_hi, ((int)rank + 1) * p.split_len);
     k_lo = k_lo / BN * BN;
@@ -401,13 +401,13 @@ paged_attn_cluster_kernel(const MmaParams p) {
         const int row = row0 + rw * 16 + (lane >> 2) + 8 * h;
         rvalid[h] = row < nrows;
         rpos[h] = rvalid[h] ? ctx + row / G : -1;
-        rlo[h] = p.window > 0 ? max(0, rpos[h] - p.window + 1) : 0;
+        rlo[h] = first_visible_key(rpos[h], p.window, p.chunk);
     }
     const int wrow_lo = row0 + rw * 16, wrow_hi = min(nrows, wrow_lo + 16) - 1;
     const bool warp_active = wrow_lo < nrows;
     const int wpos_hi = warp_active ? ctx + wrow_hi / G : -1;
     const int wpos_lo = warp_active ? ctx + wrow_lo / G : -1;
-    const int wkey_lo = p.window > 0 ? max(0, wpos_lo - p.window + 1) : 0;
+    const int wkey_lo = first_visible_key(wpos_lo, p.window, p.chunk);
 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[D / 8][4];
@@ -498,7 +498,7 @@ paged_attn_cluster_kernel(const MmaParams p) {
         group_sync();                                           // the group has read the keys: their buffer is free
         if (more) issue(kb, p.k_pages, off_next); else cp_async_commit();
         if (needed) {
-            const bool full = kt + BN - 1 <= wpos_lo && kt >= (p.window > 0 ? max(0, wpos_hi - p.window + 1) : 0) && kt + BN <= k_hi
+            const bool full = kt + BN - 1 <= wpos_lo && kt >= (first_visible_key(wpos_hi, p.window, p.chunk)) && kt + BN <= k_hi
                               && wrow_hi - wrow_lo == 15;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -777,22 +777,22 @@ extern "C" int ttie_attn_cluster_active(int D, int max_q_len, int Hq, int Hkv, i
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                             int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
+                                             int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                              float* scratch, int form, void* stream);
 
 extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_width, int page_size, const int* qsl,
                                         const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                        int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
+                                        int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                         float* scratch, void* stream) {
     return ttie_paged_attention_mma_form(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out,
-                                         T, num_seqs, Hq, Hkv, D, max_q_len, scale, softcap, window, num_splits, split_len, scratch, 0, stream);
+                                         T, num_seqs, Hq, Hkv, D, max_q_len, scale, softcap, window, chunk, num_splits, split_len, scratch, 0, stream);
 }
 
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                             int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
+                                             int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                              float* scratch, int form, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_mma_supported(D)) TTIE_FAIL("paged_attention_mma: head size %d not supported (multiples of 16 up to 128)", D);
@@ -809,7 +809,7 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     p.block_table = block_table; p.table_width = table_width; p.page_size = page_size;
     p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv;
-    p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.num_splits = num_splits; p.split_len = split_len;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;

@@ -12,7 +12,7 @@ static __device__ __align__(256) float g_noalloc_scratch[TTIE_NOALLOC_SCRATCH_FL
 extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                         const int* block_table, int table_width, int page_size, const int* qsl,
                                         const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                        int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
+                                        int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                         float* scratch, void* stream);
 
 namespace {
@@ -58,5 +58,5 @@ extern "C" int ttie_paged_attention_mma_noalloc(const void* q, long long q_strid
         if (!scratch) return -3;
     }
     return ttie_paged_attention_mma(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out,
-                                    T, num_seqs, Hq, Hkv, D, max_q_len, scale, 0.f, window, num_splits, split_len, scratch, stream);
+                                    T, num_seqs, Hq, Hkv, D, max_q_len, scale, 0.f, window, 0, num_splits, split_len, scratch, stream);
 }

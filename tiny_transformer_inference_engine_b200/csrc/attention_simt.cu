@@ -28,7 +28,7 @@ struct AttnParams {
     const int* qsl; const int* seq_lens;
     void* out;
     int num_seqs, Hq, Hkv, D;
-    float scale; int window;
+    float scale; int window, chunk;
     float softcap;                 // > 0: scores pass cap * tanh(score / cap) before mask and softmax
     int row_tiles;                 // tiles of ROWS query rows per (request, kv head)
     int num_splits, split_len;
@@ -67,7 +67,7 @@ paged_attn_simt_kernel(const AttnParams p) {
     const int tok_lo = row0 / G;
     const int tok_hi = (min(nrows, row0 + ROWS) - 1) / G;
     int k_hi = ctx + tok_hi + 1;
-    int k_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int k_lo = first_visible_key(ctx + tok_lo, p.window, p.chunk);
     if (p.num_splits > 1) {
         const int piece = piece_len(kv_len, p.num_splits, p.split_len, BK);
         k_lo = max(k_lo, split * piece);
@@ -84,7 +84,7 @@ paged_attn_simt_kernel(const AttnParams p) {
         valid[r] = row < nrows;
         const int tok = valid[r] ? row / G : 0;
         pos[r] = ctx + tok;
-        lo[r] = p.window > 0 ? max(0, pos[r] - p.window + 1) : 0;
+        lo[r] = first_visible_key(pos[r], p.window, p.chunk);
         m[r] = -INFINITY; l[r] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) o[r][i] = 0.f;
@@ -409,7 +409,7 @@ extern "C" long long ttie_attn_scratch_floats(int T, int Hq, int D, int num_spli
 extern "C" int ttie_paged_attention(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                     const int* block_table, int table_width, int page_size, const int* qsl,
                                     const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                    int max_q_len, float scale, float softcap, int window, int num_splits, int split_len,
+                                    int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                     float* scratch, int dtype, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (D % 4 || D > 512 || D <= 0) TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 512)", D);
@@ -421,7 +421,7 @@ extern "C" int ttie_paged_attention(const void* q, long long q_stride, const voi
     p.q = q; p.q_stride = q_stride; p.k_pages = k_pages; p.v_pages = v_pages;
     p.block_table = block_table; p.table_width = table_width; p.page_size = page_size;
     p.qsl = qsl; p.seq_lens = seq_lens; p.out = out;
-    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.scale = scale; p.window = window; p.softcap = softcap;
+    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.scale = scale; p.window = window; p.chunk = chunk; p.softcap = softcap;
     const int G = Hq / Hkv;
     p.row_tiles = ceil_div(max_q_len * G, ROWS);
     p.num_splits = num_splits; p.split_len = split_len;

@@ -153,7 +153,7 @@ struct AttnTcParams {
     const int* qsl; const int* seq_lens;
     __nv_bfloat16* out;
     int num_seqs, Hq, Hkv;
-    float scale_log2; int window;
+    float scale_log2; int window, chunk;
     float cap_in, cap_out;                                       // score softcap: raw score s becomes cap_out * tanh(s * cap_in) (cap_in 0: none)
     int row_tiles;
     int q_rows;                                                  // rows of the query tile that are staged (a multiple of 32 that covers every request's rows)
@@ -208,7 +208,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int ctx = kv_len - q_len;
     const int tok_lo = row0 / G, tok_hi = (min(nrows, row0 + BM) - 1) / G;
     int key_hi = ctx + tok_hi + 1;                               // exclusive
-    int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int key_lo = first_visible_key(ctx + tok_lo, p.window, p.chunk);
     const int split = blockIdx.y;
     if (p.num_splits > 1) {                                      // splits start on tile boundaries
         const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
@@ -449,7 +449,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const bool valid = row < nrows;
         const int tok = valid ? row / G : 0, g = valid ? row - tok * G : 0;
         const int pos = valid ? ctx + tok : -1;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int lo = first_visible_key(pos, p.window, p.chunk);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int SC = BN / NP, OC = D / NP;                        // score and output columns of this thread
         static_assert(SC == 32 && (OC == 32 || OC == 16), "one tcgen05.ld per tile for the scores and one for the output");
@@ -674,7 +674,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     const int rows_here = min(NT * BM, nrows - row0);
     const int tok_lo = row0 / G, tok_hi = (row0 + rows_here - 1) / G;
     int key_hi = ctx + tok_hi + 1;                               // exclusive
-    int key_lo = p.window > 0 ? max(0, ctx + tok_lo - p.window + 1) : 0;
+    int key_lo = first_visible_key(ctx + tok_lo, p.window, p.chunk);
     const int split = blockIdx.y;
     if (p.num_splits > 1) {
         const int piece = piece_len(kv_len, p.num_splits, p.split_len, BN);
@@ -740,7 +740,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             const bool valid = row < nrows;
             const int tok = valid ? row / G : 0;
             const int pos = valid ? ctx + tok : -1;
-            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const int lo = first_visible_key(pos, p.window, p.chunk);
             const uint32_t s_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + S_COL + (uint32_t)t * 128;
             const float sl2 = p.scale_log2;
             float m_run = -INFINITY, l_run = 0.f;
@@ -1153,7 +1153,7 @@ extern "C" int ttie_attn_tc_supported(int D, int page_size) {
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                        int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
                                        const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
-                                       int max_q_len, float scale, float softcap, int window, int num_splits, int split_len, float* scratch,
+                                       int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len, float* scratch,
                                        int two_tiles, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
@@ -1174,7 +1174,7 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     AttnTcParams p;
     p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.block_table = block_table; p.table_width = table_width;
     p.page_size = page_size; p.qsl = qsl; p.seq_lens = seq_lens; p.out = (__nv_bfloat16*)out;
-    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+    p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles && D <= 128 ? 2 * BM : BM);
     p.num_splits = num_splits; p.split_len = split_len;

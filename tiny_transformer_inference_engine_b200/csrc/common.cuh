@@ -37,6 +37,14 @@ __device__ __forceinline__ int piece_len(int kv_len, int num_splits, int split_l
     return min(split_len, max(share, granule));
 }
 
+// First key that a query row at position `pos` may see.  chunk > 0: the first position of the row's own chunk (chunks of `chunk`
+// positions, counted from position 0 of the sequence, whatever portion of it a step brings); else window > 0: pos - window + 1;
+// else key 0.  Monotone in pos, so a tile of rows starts at the bound of its lowest row.
+__device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    if (chunk > 0) return pos <= 0 ? 0 : pos - pos % chunk;
+    return window > 0 ? max(0, pos - window + 1) : 0;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

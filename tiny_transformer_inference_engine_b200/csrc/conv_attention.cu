@@ -1,16 +1,22 @@
 // What lies between the q/k/v projection and the paged attention kernels for attention layers whose projections pass a short
-// causal convolution, whose rotation covers only the first `rot` values of a head, and whose value size differs from the
-// key size; and the per-head output gate behind the attention kernels.
+// causal convolution, whose query and key heads are normalised, whose rotation covers only the first `rot` values of a head,
+// whose value size differs from the key size or whose values are the keys themselves; and the output gate behind the
+// attention kernels.
 //
 //   qkv_conv_rope_store   one CTA per token and head.  The token's row [q | k | v] (Hq*D + Hkv*D + Hkv*Dv channels) is convolved over
 //                         time, y_t[c] = sum_k w[k][c] * u_(t - taps + 1 + k)[c] in 32-bit (weights tap-major; inputs before
 //                         the step's first token come from the request's state row, which holds the last taps - 1 projected
-//                         rows, oldest first, and is zero for a new request), q and k are rotated at the token's position
-//                         (pairs (i, i + rot/2) or (2i, 2i + 1); cos/sin from the step's table), q is written as
-//                         [T, Hq, Dp] and k, v into the pages [page, Hkv, slot, Dp]; Dp >= max(D, Dv), the rest zero.
+//                         rows, oldest first, and is zero for a new request); with norm weights every q and k head is divided
+//                         by its root mean square (eps inside the root) and multiplied by a weight per channel that all heads
+//                         share; q and k are rotated at the token's position (pairs (i, i + rot/2) or (2i, 2i + 1); cos/sin
+//                         from the step's table); q is multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1) where a
+//                         query temperature is set; q is written as [T, Hq, Dp] and k, v into the pages
+//                         [page, Hkv, slot, Dp]; Dp >= max(D, Dv), the rest zero.  v_from_k: the row has no v columns and a
+//                         value head is the key head as it stands before norm and rotation.
 //   conv_tail_update      moves the step's last taps - 1 projected rows into the state rows (a request that brought fewer
 //                         keeps the newest of its old ones); runs after the kernel above has read the old rows.
-//   gate_head_rows        out[t, h, :Dv] = attn[t, h, :Dv] * sigmoid(gate[t, h]) (gate optional), dropping the padding.
+//   gate_head_rows        out[t, h, :Dv] = attn[t, h, :Dv] * sigmoid(gate) (gate optional: one number per head, gate[t, h], or
+//                         one per value, gate[t, h * Dv + j]), dropping the padding.
 #include "common.cuh"
 using namespace ttie;
 
@@ -24,9 +30,21 @@ struct QkvArgs {
     int taps; const float* conv_w; const float* tail; int tail_rows;
     const int* positions; const int* token_seq; const int* qsl; const int* slot_ids;
     const float2* cs; int rot; int style;
+    const float* norm_w; float norm_eps;                            // [2][D]: the query heads' weights, then the key heads'; null: no norm
+    int v_from_k;                                                   // the values are the key heads before norm and rotation
+    float qt_coef; int qt_every;                                    // query temperature; every 0: none
     void* q_out; void* k_pages; void* v_pages;
     const int* block_table; int table_width, page_size, num_pages, write_kv;
 };
+
+// channels of a row [q | k | v], or [q | k] where the values are the keys
+__device__ __forceinline__ int row_channels(const QkvArgs& a) { return a.Hq * a.D + a.Hkv * a.D + (a.v_from_k ? 0 : a.Hkv * a.Dv); }
+// first channel of value head h
+__device__ __forceinline__ int value_col0(const QkvArgs& a, int h) { return a.v_from_k ? a.Hq * a.D + h * a.D : (a.Hq + a.Hkv) * a.D + h * a.Dv; }
+// what a query at position pos is multiplied by
+__device__ __forceinline__ float query_temperature(const QkvArgs& a, int pos) {
+    return a.qt_every > 0 ? 1.0f + a.qt_coef * logf((float)((pos + 1) / a.qt_every) + 1.0f) : 1.0f;
+}
 
 // value i of a head row x after the rotation of its first `rot` values
 __device__ __forceinline__ float rotated(const float* x, int i, int rot, int style, const float2* cs) {
@@ -46,12 +64,13 @@ template <typename T>
 __global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs a) {
     TTIE_PDL_ENTRY();
     extern __shared__ float row[];                                  // the head's convolved channels
+    __shared__ float red[32];
     const int t = blockIdx.x, unit = blockIdx.y;
-    const int C = a.Hq * a.D + a.Hkv * a.D + a.Hkv * a.Dv;
+    const int C = row_channels(a);
     const int kind = unit < a.Hq ? 0 : unit < a.Hq + a.Hkv ? 1 : 2; // q, k, v
     const int h = kind == 0 ? unit : kind == 1 ? unit - a.Hq : unit - a.Hq - a.Hkv;
     const int width = kind == 2 ? a.Dv : a.D;
-    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : (a.Hq + a.Hkv) * a.D + h * a.Dv;
+    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : value_col0(a, h);
     if (kind != 0 && !a.write_kv) return;
     const T* proj = reinterpret_cast<const T*>(a.proj);
     const int s = a.token_seq[t];
@@ -75,14 +94,23 @@ __global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs 
         }
     }
     __syncthreads();
+    if (a.norm_w && kind != 2) {                                    // the head over its root mean square, times the shared weight
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < a.D; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
+        for (int i = threadIdx.x; i < a.D; i += blockDim.x) row[i] = row[i] * inv * a.norm_w[kind * a.D + i];
+        __syncthreads();
+    }
     const float2* cs = a.rot > 0 ? a.cs + (size_t)t * (a.rot >> 1) : nullptr;
+    const int pos = a.positions[t];
     if (kind == 0) {
         T* q = reinterpret_cast<T*>(a.q_out) + ((size_t)t * a.Hq + h) * a.Dp;
+        const float temp = query_temperature(a, pos);
         for (int i = threadIdx.x; i < a.Dp; i += blockDim.x)
-            q[i] = from_f32<T>(i < a.D ? rotated(row, i, a.rot, a.style, cs) : 0.f);
+            q[i] = from_f32<T>(i < a.D ? rotated(row, i, a.rot, a.style, cs) * temp : 0.f);
         return;
     }
-    const int pos = a.positions[t];
     int page = a.block_table[(size_t)s * a.table_width + pos / a.page_size];
     if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
     const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + pos % a.page_size) * a.Dp;
@@ -100,7 +128,8 @@ __global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs 
 // ---- bfloat16, eight values per thread: no shared memory, no barrier, so that prompt portions run as a few waves of threads
 // each with all its loads in flight.  A thread owns eight consecutive values of one head of one token; inside the rotated
 // part it convolves its partner's eight values as well (pairs (i, i + rot/2): the chunk rot/2 away; pairs (2i, 2i + 1): its own).
-// Sizes: D, Dv, Dp and the row stride multiples of 8; rot a multiple of 16 (half pairs) or of 8 (interleaved pairs).
+// Sizes: D, Dv, Dp and the row stride multiples of 8; rot a multiple of 16 (half pairs) or of 8 (interleaved pairs).  With a
+// query/key norm the threads of a head (Dp / 8 adjacent lanes, a power of two) add their squares up by shuffles.
 __device__ __forceinline__ void conv8(const QkvArgs& a, const __nv_bfloat16* __restrict__ proj, const float* __restrict__ tail, int C,
                                       int t, int j, int c, float* acc) {
 #pragma unroll
@@ -139,45 +168,73 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const Qkv
     const int jc = (int)(id % chunks);
     const int unit = (int)((id / chunks) % units);
     const int t = (int)(id / ((long long)chunks * units));
-    const int C = a.Hq * a.D + a.Hkv * a.D + a.Hkv * a.Dv;
+    const int C = row_channels(a);
     const int kind = unit < a.Hq ? 0 : unit < a.Hq + a.Hkv ? 1 : 2;
     const int h = kind == 0 ? unit : kind == 1 ? unit - a.Hq : unit - a.Hq - a.Hkv;
     if (kind != 0 && !a.write_kv) return;
     const int width = kind == 2 ? a.Dv : a.D;
-    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : (a.Hq + a.Hkv) * a.D + h * a.Dv;
+    const int c0 = kind == 0 ? h * a.D : kind == 1 ? a.Hq * a.D + h * a.D : value_col0(a, h);
     const int i0 = jc << 3;                                          // first of this thread's values within the head
     const __nv_bfloat16* proj = reinterpret_cast<const __nv_bfloat16*>(a.proj);
     const int s = a.token_seq[t];
+    const int j = t - a.qsl[s];
+    const float* tail = a.taps > 1 ? a.tail + (size_t)slot_row_(a.slot_ids[s], a.tail_rows) * (a.taps - 1) * C : nullptr;
+    const bool inside = i0 < width;
     float out[8];
-    if (i0 >= width) {
+    if (inside) conv8(a, proj, tail, C, t, j, c0 + i0, out);
+    else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) out[i] = 0.f;
-    } else {
-        const int j = t - a.qsl[s];
-        const float* tail = a.taps > 1 ? a.tail + (size_t)slot_row_(a.slot_ids[s], a.tail_rows) * (a.taps - 1) * C : nullptr;
-        conv8(a, proj, tail, C, t, j, c0 + i0, out);
-        if (kind != 2 && i0 < a.rot) {
-            const float2* cs = a.cs + (size_t)t * (a.rot >> 1);
-            if (a.style == 1) {
-                const int half = a.rot >> 1;
-                const bool low = i0 < half;
-                float other[8];
-                conv8(a, proj, tail, C, t, j, c0 + (low ? i0 + half : i0 - half), other);
-                const int f0 = low ? i0 : i0 - half;
+    }
+    float inv = 1.f;
+    const bool normed = a.norm_w != nullptr && kind != 2;
+    if (normed) {                                                    // (the same for all lanes of a head: they sit side by side)
+        float ss = 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 c = cs[f0 + i];
-                    out[i] = low ? out[i] * c.x - other[i] * c.y : out[i] * c.x + other[i] * c.y;
-                }
-            } else {
+        for (int i = 0; i < 8; ++i) ss = fmaf(out[i], out[i], ss);
+        const unsigned lane = threadIdx.x & 31u;
+        const unsigned group = chunks >= 32 ? 0xffffffffu : ((1u << chunks) - 1u) << (lane & ~(unsigned)(chunks - 1));
+        for (int o = 1; o < chunks; o <<= 1) ss += __shfl_xor_sync(group, ss, o);
+        inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
+        if (inside) {
+            const float* w = a.norm_w + kind * a.D + i0;
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const float2 c = cs[(i0 + i) >> 1];
-                    const float x = out[i], y = out[i + 1];
-                    out[i] = x * c.x - y * c.y; out[i + 1] = x * c.y + y * c.x;
-                }
+            for (int i = 0; i < 8; ++i) out[i] = out[i] * inv * w[i];
+        }
+    }
+    if (inside && kind != 2 && i0 < a.rot) {
+        const float2* cs = a.cs + (size_t)t * (a.rot >> 1);
+        if (a.style == 1) {
+            const int half = a.rot >> 1;
+            const bool low = i0 < half;
+            const int ip = low ? i0 + half : i0 - half;              // the partner's first value
+            float other[8];
+            conv8(a, proj, tail, C, t, j, c0 + ip, other);
+            if (normed) {
+                const float* w = a.norm_w + kind * a.D + ip;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) other[i] = other[i] * inv * w[i];
+            }
+            const int f0 = low ? i0 : i0 - half;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 c = cs[f0 + i];
+                out[i] = low ? out[i] * c.x - other[i] * c.y : out[i] * c.x + other[i] * c.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const float2 c = cs[(i0 + i) >> 1];
+                const float x = out[i], y = out[i + 1];
+                out[i] = x * c.x - y * c.y; out[i + 1] = x * c.y + y * c.x;
             }
         }
+    }
+    const int pos = a.positions[t];
+    if (kind == 0 && a.qt_every > 0) {
+        const float temp = query_temperature(a, pos);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] *= temp;
     }
     uint4 packed;
     __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&packed);
@@ -187,7 +244,6 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const Qkv
         *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.q_out) + ((size_t)t * a.Hq + h) * a.Dp + i0) = packed;
         return;
     }
-    const int pos = a.positions[t];
     int page = a.block_table[(size_t)s * a.table_width + pos / a.page_size];
     if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
     const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + pos % a.page_size) * a.Dp + i0;
@@ -210,34 +266,44 @@ __global__ void conv_tail_update_kernel(const T* __restrict__ proj, long long ld
 }
 
 template <typename T>
-__global__ void gate_head_rows_kernel(const T* __restrict__ attn, const T* __restrict__ gate, long long ld_gate, int T_, int H, int Dv,
-                                      int Dp, T* __restrict__ out) {
+__global__ void gate_head_rows_kernel(const T* __restrict__ attn, const T* __restrict__ gate, long long ld_gate, int per_value, int T_, int H,
+                                      int Dv, int Dp, T* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const int col = blockIdx.x * blockDim.x + threadIdx.x;           // grid: (columns of a token's output row, tokens)
     if (col >= H * Dv) return;
     const int h = col / Dv, j = col - h * Dv;
     for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
         float v = to_f32(attn[(t * H + h) * Dp + j]);
-        if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[t * ld_gate + h])));
+        if (gate) v *= 1.0f / (1.0f + expf(-to_f32(gate[t * ld_gate + (per_value ? col : h)])));
         out[t * H * Dv + col] = from_f32<T>(v);
     }
 }
 
 // bfloat16, eight values per thread (value size and padded size multiples of 8, 16-byte aligned rows)
 __global__ void gate_head_rows_vec8_kernel(const __nv_bfloat16* __restrict__ attn, const __nv_bfloat16* __restrict__ gate, long long ld_gate,
-                                           int T_, int H, int Dv, int Dp, __nv_bfloat16* __restrict__ out) {
+                                           int per_value, int T_, int H, int Dv, int Dp, __nv_bfloat16* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (col >= H * Dv) return;
     const int h = col / Dv, j = col - h * Dv;
     for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
         const uint4 x = *reinterpret_cast<const uint4*>(attn + (t * H + h) * Dp + j);
-        const float g = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld_gate + h]))) : 1.0f;
         uint4 y;
         const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&x);
         __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&y);
+        if (gate && per_value) {                                     // (the gate row is 16-byte aligned like the others: the caller checks)
+            const uint4 gv = *reinterpret_cast<const uint4*>(gate + t * ld_gate + col);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(a[i]); b[i] = __floats2bfloat162_rn(f.x * g, f.y * g); }
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(a[i]), g = __bfloat1622float2(g2[i]);
+                b[i] = __floats2bfloat162_rn(f.x / (1.0f + expf(-g.x)), f.y / (1.0f + expf(-g.y)));
+            }
+        } else {
+            const float g = gate ? 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld_gate + h]))) : 1.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(a[i]); b[i] = __floats2bfloat162_rn(f.x * g, f.y * g); }
+        }
         *reinterpret_cast<uint4*>(out + t * H * Dv + col) = y;
     }
 }
@@ -247,9 +313,12 @@ __global__ void gate_head_rows_vec8_kernel(const __nv_bfloat16* __restrict__ att
 extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, int Hq, int Hkv, int D, int Dv, int Dp, int taps,
                                         const float* conv_w, const float* tail, int tail_rows, const int* positions,
                                         const int* token_seq, const int* qsl, const int* slot_ids, const void* cs, int rot, int style,
+                                        const float* norm_w, float norm_eps, int v_from_k, float qt_coef, int qt_every,
                                         void* q_out, void* k_pages, void* v_pages, const int* block_table, int table_width,
                                         int page_size, int num_pages, int write_kv, int dtype, void* stream) {
     if (T <= 0) return 0;
+    if (v_from_k && Dv != D) TTIE_FAIL("qkv_conv_rope_store: values that are the keys have the keys' size, not %d against %d", Dv, D);
+    if (qt_every < 0) TTIE_FAIL("qkv_conv_rope_store: a query temperature every %d positions", qt_every);
     if (Dp < D || Dp < Dv) TTIE_FAIL("qkv_conv_rope_store: padded head size %d below %d / %d", Dp, D, Dv);
     if (rot < 0 || rot > D || rot % 2) TTIE_FAIL("qkv_conv_rope_store: %d rotated values of a head of %d", rot, D);
     if (rot > 0 && !cs) TTIE_FAIL("qkv_conv_rope_store: a rotation needs the step's cos/sin table");
@@ -257,13 +326,17 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     QkvArgs a;
     a.proj = proj; a.ld = ld; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.Dv = Dv; a.Dp = Dp; a.taps = taps; a.conv_w = conv_w; a.tail = tail;
     a.tail_rows = tail_rows; a.positions = positions; a.token_seq = token_seq; a.qsl = qsl; a.slot_ids = slot_ids;
-    a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
+    a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.norm_w = norm_w; a.norm_eps = norm_eps; a.v_from_k = v_from_k;
+    a.qt_coef = qt_coef; a.qt_every = qt_every; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
     a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.write_kv = write_kv;
     const size_t smem = (size_t)(D > Dv ? D : Dv) * sizeof(float);
     if (T > 2147483647 / 1 || Hq + 2 * Hkv > 65535) TTIE_FAIL("qkv_conv_rope_store: %d heads exceed the grid", Hq + 2 * Hkv);
     cudaStream_t s = (cudaStream_t)stream;
     const bool aligned = !(((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)conv_w | (uintptr_t)tail) & 15);
-    if (dtype == kBF16 && D % 8 == 0 && Dv % 8 == 0 && Dp % 8 == 0 && ld % 8 == 0 && aligned && (rot == 0 || rot % (style == 1 ? 16 : 8) == 0)) {
+    const int lanes = Dp / 8;                                        // of a head in the eight-values form; a norm adds up over them by shuffles
+    const bool norm_ok = !norm_w || (Dp % 8 == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0);
+    if (dtype == kBF16 && D % 8 == 0 && Dv % 8 == 0 && Dp % 8 == 0 && ld % 8 == 0 && aligned && norm_ok
+        && (rot == 0 || rot % (style == 1 ? 16 : 8) == 0)) {
         const long long threads = (long long)T * (Hq + 2 * Hkv) * (Dp / 8);
         if ((threads + 255) / 256 > 2147483647LL) TTIE_FAIL("qkv_conv_rope_store: grid too large");
         TTIE_LAUNCH(qkv_conv_rope_store_vec8_kernel, (unsigned)((threads + 255) / 256), 256, 0, s, a, T);
@@ -290,20 +363,21 @@ extern "C" int ttie_conv_tail_update(const void* proj, long long ld, int C, int 
     return 0;
 }
 
-extern "C" int ttie_gate_head_rows(const void* attn, const void* gate, long long ld_gate, int T, int H, int Dv, int Dp, void* out,
-                                   int dtype, void* stream) {
+extern "C" int ttie_gate_head_rows(const void* attn, const void* gate, long long ld_gate, int per_value, int T, int H, int Dv, int Dp,
+                                   void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(ceil_div(H * Dv, 256), T < 65535 ? T : 65535);
-    if (dtype == kBF16 && Dv % 8 == 0 && Dp % 8 == 0 && !(((uintptr_t)attn | (uintptr_t)out) & 15)) {
+    if (dtype == kBF16 && Dv % 8 == 0 && Dp % 8 == 0 && !(((uintptr_t)attn | (uintptr_t)out) & 15)
+        && !(gate && per_value && (((uintptr_t)gate & 15) || ld_gate % 8))) {
         dim3 g8(ceil_div(H * Dv / 8, 128), T < 65535 ? T : 65535);
-        TTIE_LAUNCH(gate_head_rows_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, T, H, Dv, Dp,
-                    (__nv_bfloat16*)out);
+        TTIE_LAUNCH(gate_head_rows_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, per_value, T, H,
+                    Dv, Dp, (__nv_bfloat16*)out);
         TTIE_CHECK_LAUNCH("gate_head_rows");
         return 0;
     }
-    if (dtype == kF32) TTIE_LAUNCH(gate_head_rows_kernel<float>, grid, 256, 0, s, (const float*)attn, (const float*)gate, ld_gate, T, H, Dv, Dp, (float*)out);
-    else if (dtype == kBF16) TTIE_LAUNCH(gate_head_rows_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, T, H, Dv, Dp, (__nv_bfloat16*)out);
+    if (dtype == kF32) TTIE_LAUNCH(gate_head_rows_kernel<float>, grid, 256, 0, s, (const float*)attn, (const float*)gate, ld_gate, per_value, T, H, Dv, Dp, (float*)out);
+    else if (dtype == kBF16) TTIE_LAUNCH(gate_head_rows_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)attn, (const __nv_bfloat16*)gate, ld_gate, per_value, T, H, Dv, Dp, (__nv_bfloat16*)out);
     else TTIE_FAIL("gate_head_rows: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("gate_head_rows");
     return 0;

@@ -49,22 +49,23 @@ extern "C" int ttie_abi_version() { return 4; }
 // ------------------------------------------------------------------------------------------ embed
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
-                             int d, int vocab) {
+                             int d, int vocab, float scale) {
     TTIE_PDL_ENTRY();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);          // ids are validated on the host; never read outside
     const T* row = table + (size_t)id * d;
     float* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
 }
 
-extern "C" int ttie_embed(const int* ids, const void* table, float* out, int T, int d, int vocab, int dtype, void* stream) {
+// out[t, :] = table[ids[t], :] * scale, 32-bit
+extern "C" int ttie_embed(const int* ids, const void* table, float* out, int T, int d, int vocab, float scale, int dtype, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
-    if (dtype == kF32) TTIE_LAUNCH(embed_kernel<float>, T, threads, 0, s, ids, (const float*)table, out, d, vocab);
-    else if (dtype == kBF16) TTIE_LAUNCH(embed_kernel<__nv_bfloat16>, T, threads, 0, s, ids, (const __nv_bfloat16*)table, out, d, vocab);
+    if (dtype == kF32) TTIE_LAUNCH(embed_kernel<float>, T, threads, 0, s, ids, (const float*)table, out, d, vocab, scale);
+    else if (dtype == kBF16) TTIE_LAUNCH(embed_kernel<__nv_bfloat16>, T, threads, 0, s, ids, (const __nv_bfloat16*)table, out, d, vocab, scale);
     else TTIE_FAIL("embed: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("embed");
     return 0;

@@ -1,8 +1,9 @@
 // Recurrent layers whose per-head state is a matrix S [key channels x value channels] that every token updates by a rank-one
-// term: the RWKV-style time mix with a decay per key channel (wkv) and the xLSTM matrix memory with scalar gates and a running
-// maximum (mlstm).  All of a recurrence is 32-bit: decays, gates, exponentials, the state and the read-out.
+// term: the RWKV-style time mix with a decay per key channel (wkv), the xLSTM matrix memory with scalar gates and a running
+// maximum (mlstm), and retention, linear attention with one fixed decay per head and neither softmax nor denominator.  All of
+// a recurrence is 32-bit: decays, gates, exponentials, rotated queries and keys, the state and the read-out.
 //
-// Both scans share one layout.  A value column of S moves independently of the others, so a thread owns KPT consecutive key
+// The scans share one layout.  A value column of S moves independently of the others, so a thread owns KPT consecutive key
 // channels of one column (KPT = 4 for heads of up to 128 key channels, 8 up to 256, 16 up to 512: the fewest whose slices fit
 // a warp, because the recurrence offers no other parallelism than its state's elements): a CTA is (columns x slices) threads
 // for one (request, head), slices = key channels / KPT rounded up to a power of two, the lanes of a column's slices adjacent
@@ -20,7 +21,10 @@
 //   mlstm_gates       i = cap tanh(i'/cap), f = logsigmoid(cap tanh(f'/cap)), m' = max(f + m, i) as prefix operations of a warp;
 //                     per token e^(f+m-m'), e^(i-m'), e^(-m'); also copies the normaliser state n for the scan to read
 //   mlstm_scan        S <- e^(f+m-m') S + e^(i-m') k v^T, n likewise with k alone, o = S^T q / (max(|n.q|, e^(-m')) + 1e-6)
-//   head_norm_gate    out = o / rms(o over the head) * weight * act(gate)   (act: silu or sigmoid)
+//   rotate_heads      float32 copies of `heads` head rows per token with the first `rot` values of each rotated at the token's
+//                     position (either pairing) and the heads from `scale_from` on multiplied by a constant
+//   retention_scan    S <- decay_h S + k v^T, o = S^T q, with q and k 32-bit (already rotated and scaled)
+//   head_norm_gate    out = o / rms(o over the head) * weight * act(gate)   (act: silu or sigmoid; the weight is optional)
 #include "common.cuh"
 #include <math.h>
 using namespace ttie;
@@ -528,6 +532,158 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
     }
 }
 
+// ---- retention
+// float32 copies of head rows with the first `rot` values of each head rotated at the token's position: src [T, ld] holds
+// `heads` rows of D values per token from column 0 on; cs [T, rot / 2] (cos, sin); style 0 pairs (2i, 2i + 1), 1 pairs
+// (i, i + rot / 2).  Heads from `scale_from` on are multiplied by `scale` after the rotation.  One thread per value.
+template <typename T>
+__global__ void rotate_heads_kernel(const T* __restrict__ src, long long ld, int T_, int heads, int D, int rot, int style,
+                                    const float2* __restrict__ cs, int scale_from, float scale, float* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const long long total = (long long)T_ * heads * D;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int i = (int)(e % D);
+        const int h = (int)((e / D) % heads);
+        const long long t = e / ((long long)D * heads);
+        const T* x = src + t * ld + (size_t)h * D;
+        float v = to_f32(x[i]);
+        if (i < rot) {
+            const int half = rot >> 1;
+            const float2* c = cs + t * half;
+            if (style == 1) {
+                if (i < half) v = v * c[i].x - to_f32(x[i + half]) * c[i].y;
+                else v = v * c[i - half].x + to_f32(x[i - half]) * c[i - half].y;
+            } else {
+                const float2 cc = c[i >> 1];
+                v = (i & 1) ? v * cc.x + to_f32(x[i - 1]) * cc.y : v * cc.x - to_f32(x[i + 1]) * cc.y;
+            }
+        }
+        out[e] = h >= scale_from ? v * scale : v;
+    }
+}
+
+struct RetArgs {
+    const float* q; const float* k; long long ld_qk;                  // [T, H*D] each, float32, one row stride
+    const void* v; long long ld_v;                                    // [T, H*Dv], compute dtype
+    const float* decay;                                               // [H]
+    float* S; int state_rows;                                         // [rows, H, Dv, Dpad]
+    const int* qsl; const int* slot_ids;
+    float* out;                                                       // [T, H*Dv] float32
+    int H, D, Dv, Dpad, slices, tb; bool vec;
+};
+
+template <typename T, int KPT, int SL>
+__global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
+    pdl_wait();                                                      // (the successor is let in at the end, as in the other scans)
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int TB = 64 / KPT;
+    const int cols = blockDim.x / SL;
+    float* q_s = reinterpret_cast<float*>(smem_raw);                                  // [2][TB][Dpad]
+    float* k_s = q_s + 2 * TB * a.Dpad;
+    float* v_s = k_s + 2 * TB * a.Dpad;                                               // [TB][cols]
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
+    const int slice = threadIdx.x % SL, cl = threadIdx.x / SL;
+    const int col = blockIdx.x * cols + cl;
+    const bool colv = col < a.Dv;
+    const int ch0 = slice * KPT;
+    const size_t row = slot_row_(a.slot_ids[s], a.state_rows);
+    float* sp = a.S + ((row * a.H + h) * a.Dv + (colv ? col : 0)) * a.Dpad + ch0;
+    float S[KPT];
+#pragma unroll
+    for (int i = 0; i < KPT; i += 4) {
+        const float4 x4 = colv ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[i] = x4.x; S[i + 1] = x4.y; S[i + 2] = x4.z; S[i + 3] = x4.w;
+    }
+    const float decay = a.decay[h];
+    const float* qp = a.q + (size_t)t0 * a.ld_qk + h * a.D;
+    const float* kp = a.k + (size_t)t0 * a.ld_qk + h * a.D;
+    const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld_v + h * a.Dv;
+    const size_t ld_o = (size_t)a.H * a.Dv;
+    if (n <= DIRECT_TOKENS) {
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = colv ? to_f32(vp[(size_t)tt * a.ld_v + col]) : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) {
+                const bool in = ch0 + i < a.D;
+                const float kv = (in ? kp[(size_t)tt * a.ld_qk + ch0 + i] : 0.f) * vj;
+                S[i] = fmaf(decay, S[i], kv);
+                acc = fmaf(S[i], in ? qp[(size_t)tt * a.ld_qk + ch0 + i] : 0.f, acc);
+            }
+            acc = slices_sum<SL>(acc);
+            if (slice == 0 && colv) a.out[(size_t)(t0 + tt) * ld_o + h * a.Dv + col] = acc;
+        }
+    } else {
+    if (a.Dpad > a.D)
+        for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
+            if (e % a.Dpad >= a.D) { q_s[e] = 0.f; k_s[e] = 0.f; }
+    auto stage = [&](int buf, int c0, int nb) {
+        stage_rows<float>(q_s + buf * TB * a.Dpad, a.Dpad, qp + (size_t)c0 * a.ld_qk, a.ld_qk, nb, a.D, a.vec);
+        stage_rows<float>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld_qk, a.ld_qk, nb, a.D, a.vec);
+        cp_async_commit();
+    };
+    float vreg[MAXV];                                                // this thread's share of the next run's v
+    auto fetch_v = [&](int c0, int nb) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) {
+                const int tt = e / cols, c = blockIdx.x * cols + (e - tt * cols);
+                vreg[i] = c < a.Dv ? to_f32(vp[(size_t)(c0 + tt) * a.ld_v + c]) : 0.f;
+            }
+        }
+    };
+    stage(0, 0, min(TB, n));
+    fetch_v(0, min(TB, n));
+    for (int c0 = 0, it = 0; c0 < n; c0 += TB, ++it) {
+        const int nb = min(TB, n - c0), buf = it & 1;
+        const bool more = c0 + TB < n;
+        if (more) stage(buf ^ 1, c0 + TB, min(TB, n - c0 - TB));
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int e = i * blockDim.x + threadIdx.x;
+            if (e < nb * cols) v_s[e] = vreg[i];
+        }
+        if (more) { fetch_v(c0 + TB, min(TB, n - c0 - TB)); cp_async_wait<1>(); } else cp_async_wait<0>();
+        __syncthreads();
+        const float* qb = q_s + buf * TB * a.Dpad + ch0;
+        const float* kb = k_s + buf * TB * a.Dpad + ch0;
+        float part[TB];                                              // this thread's share of every token's read-out
+#pragma unroll
+        for (int tt = 0; tt < TB; ++tt) {
+            part[tt] = 0.f;
+            if (tt < nb) {                                           // (the same for every thread of the CTA)
+                const float vj = v_s[tt * cols + cl];
+                float q_[KPT], k_[KPT];
+                lds_keys<KPT>(qb + tt * a.Dpad, q_);
+                lds_keys<KPT>(kb + tt * a.Dpad, k_);
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    S[i] = fmaf(decay, S[i], k_[i] * vj);
+                    acc = fmaf(S[i], q_[i], acc);
+                }
+                part[tt] = acc;
+            }
+        }
+        int first = 0;
+        RunReduce<SL / 2, TB>::run(part, slice, first);
+        if (colv && RunOwner<SL, TB>::writes(slice)) {
+#pragma unroll
+            for (int j = 0; j < RunOwner<SL, TB>::COUNT; ++j)
+                if (first + j < nb) a.out[(size_t)(t0 + c0 + first + j) * ld_o + h * a.Dv + col] = part[j];
+        }
+        __syncthreads();
+    }
+    }
+    pdl_launch_dependents();
+    if (colv) {
+#pragma unroll
+        for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+    }
+}
+
 // one warp per (token, head)
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long ld_g, const float* __restrict__ w,
@@ -546,7 +702,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __re
     for (int j = lane; j < Dv; j += 32) {
         const float g = to_f32(gate[(size_t)t * ld_g + h * Dv + j]);
         const float sg = 1.0f / (1.0f + expf(-g));
-        out[(size_t)unit * Dv + j] = from_f32<T>(src[j] * inv * w[h * Dv + j] * (act == 0 ? g * sg : sg));
+        out[(size_t)unit * Dv + j] = from_f32<T>(src[j] * inv * (w ? w[h * Dv + j] : 1.0f) * (act == 0 ? g * sg : sg));
     }
 }
 
@@ -677,6 +833,43 @@ extern "C" int ttie_mlstm_scan(const void* q, const void* k, const void* v, long
     cudaStream_t s = (cudaStream_t)stream;
     TTIE_SCAN_DISPATCH(mlstm_scan_kernel, MlstmArgs);
     TTIE_CHECK_LAUNCH("mlstm_scan");
+    return 0;
+}
+
+extern "C" int ttie_rotate_heads(const void* src, long long ld, int T, int heads, int D, int rot, int style, const void* cs,
+                                 int scale_from, float scale, float* out, int dtype, void* stream) {
+    if (T <= 0 || heads <= 0) return 0;
+    if (rot < 0 || rot > D || rot % 2) TTIE_FAIL("rotate_heads: %d rotated values of a head of %d", rot, D);
+    if (rot > 0 && !cs) TTIE_FAIL("rotate_heads: a rotation needs the step's cos/sin table");
+    const long long total = (long long)T * heads * D;
+    const int grid = (int)((total + 255) / 256 < 148LL * 32 ? (total + 255) / 256 : 148LL * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kF32) TTIE_LAUNCH(rotate_heads_kernel<float>, grid, 256, 0, s, (const float*)src, ld, T, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
+    else if (dtype == kBF16) TTIE_LAUNCH(rotate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)src, ld, T, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
+    else TTIE_FAIL("rotate_heads: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("rotate_heads");
+    return 0;
+}
+
+extern "C" int ttie_retention_scan(const float* q, const float* k, long long ld_qk, const void* v, long long ld_v, const float* decay,
+                                   float* S, int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D,
+                                   int Dv, int dtype, void* stream) {
+    if (num_seqs <= 0) return 0;
+    RetArgs a;
+    a.q = q; a.k = k; a.ld_qk = ld_qk; a.v = v; a.ld_v = ld_v; a.decay = decay; a.S = S; a.state_rows = state_rows;
+    a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv;
+    int threads, kpt;
+    if (scan_shape(D, Dv, num_seqs * H, &kpt, &a.slices, &threads)) TTIE_FAIL("retention_scan: %d key channels per head (at most 512)", D);
+    a.Dpad = a.slices * kpt;
+    const int cols = threads / a.slices;
+    a.tb = 64 / kpt;
+    if (threads * MAXV < a.tb * cols) TTIE_FAIL("retention_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
+    const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * 4 + (size_t)a.tb * cols * 4;
+    a.vec = D % 4 == 0 && ld_qk % 4 == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
+    dim3 grid(ceil_div(Dv, cols), H, num_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    TTIE_SCAN_DISPATCH(retention_scan_kernel, RetArgs);
+    TTIE_CHECK_LAUNCH("retention_scan");
     return 0;
 }
 

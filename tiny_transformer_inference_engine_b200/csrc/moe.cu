@@ -1,15 +1,19 @@
 // Gated linear units with their constants as parameters, and a routed mixture of experts.
 //   glu:            y = g' * sigmoid(alpha * g') * (u' + shift), g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0:
 //                   no clamp); alpha = 1, shift = 0 is SwiGLU.  32-bit arithmetic, rounded once.
-//   moe_route:      scores s = sigmoid(z) from 32-bit router logits; expert e is in group
-//                   e / (E / groups); a group is rated by adding up its `group_top` highest scores, the `keep` best-rated
-//                   groups stay eligible; the `top` highest scores among eligible experts are taken (ties: the lower index),
+//   moe_route:      scores s = sigmoid(z), or softmax(z) over all experts, from 32-bit router logits; the choice is made by
+//                   c = s + correction (a bias per expert, optional), the weights use s alone; expert e is in group
+//                   e / (E / groups); a group is rated by adding up its `group_top` highest c, the `keep` best-rated
+//                   groups stay eligible; the `top` highest c among eligible experts are taken (ties: the lower index),
 //                   weighted s * scale, optionally renormalised to sum to `scale`.  One warp per token, all 32-bit.
 //   moe_plan:       counting sort of the (token, choice) pairs by expert, on the device: offsets per expert, position of each
 //                   pair, and a table of row tiles (expert, first row, rows) for the grouped product; nothing is read on the host.
+//                   Only the first `tile_experts` experts get tiles: the ones behind them are identity experts, which own no
+//                   matrices (their pairs are sorted like the others and no product touches their rows).
 //   grouped_gemm:   C[pos, :] = A[row_of(pos), :] * W[expert_of_tile]^T for every tile of the table (FFMA, 32-bit accumulation,
 //                   any sizes; operands in the compute dtype).
-//   moe_combine:    out[t, :] = sum_k weight[t, k] * Y[pos(t, k), :] (+ shared[t, :]) in 32-bit, in the order of k.
+//   moe_combine:    out[t, :] = sum_k weight[t, k] * Y[pos(t, k), :] (+ shared[t, :]) in 32-bit, in the order of k; a choice k
+//                   whose expert is an identity expert (idx >= first_identity) adds weight[t, k] * x[t, :] instead.
 #include "common.cuh"
 using namespace ttie;
 
@@ -61,22 +65,35 @@ constexpr int MAX_EXPERTS = 512;
 constexpr int ROUTE_WARPS = 4;
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, int keep, int group_top, int top,
-                 float scale, int renorm, int* __restrict__ idx, float* __restrict__ wts) {
+                 float scale, int renorm, int softmax, const float* __restrict__ correction, int* __restrict__ idx,
+                 float* __restrict__ wts) {
     extern __shared__ float sm[];
     TTIE_PDL_ENTRY();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * ROUTE_WARPS + warp;
     if (t >= T_) return;                                             // (whole warps leave; nothing below synchronises the block)
-    float* s = sm + (size_t)warp * (E + 2 * groups);
-    float* rating = s + E;
+    float* s = sm + (size_t)warp * (2 * E + 2 * groups);             // the scores (weights), then what the choice is made by
+    float* c = s + E;
+    float* rating = c + E;
     float* kept = rating + groups;
     const int per = E / groups;
-    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+    if (softmax) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logits[(size_t)t * E + e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(logits[(size_t)t * E + e] - mx); s[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
+    } else {
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+    }
+    for (int e = lane; e < E; e += 32) c[e] = correction ? s[e] + correction[e] : s[e];
     __syncwarp();
-    for (int g = lane; g < groups; g += 32) {                        // a group's rating: the sum of its `group_top` (1 or 2) highest scores
-        float b0 = -1.f, b1 = -1.f;
+    for (int g = lane; g < groups; g += 32) {                        // a group's rating: the sum of its `group_top` (1 or 2) highest values
+        float b0 = -INFINITY, b1 = -INFINITY;
         for (int e = 0; e < per; ++e) {
-            const float v = s[g * per + e];
+            const float v = c[g * per + e];
             if (v > b0) { b1 = b0; b0 = v; } else if (v > b1) b1 = v;
         }
         rating[g] = b0 + ((group_top > 1 && per > 1) ? b1 : 0.f);
@@ -90,19 +107,22 @@ moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, in
     __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
-        float bv = -1.f;
+        float bv = -INFINITY;
         int be = -1;
-        for (int e = lane; e < E; e += 32)
-            if (kept[e / per] != 0.f && s[e] > bv) { bv = s[e]; be = e; }      // (taken scores are -1; ascending e: the lower index wins a tie)
+        for (int e = lane; e < E; e += 32)                             // (taken experts are marked NaN and never compare greater; ascending e: the lower index wins a tie)
+            if (kept[e / per] != 0.f && c[e] == c[e] && (be < 0 || c[e] > bv)) { bv = c[e]; be = e; }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-            if (oe >= 0 && (ov > bv || (ov == bv && (be < 0 || oe < be)))) { bv = ov; be = oe; }
+            if (oe >= 0 && (be < 0 || ov > bv || (ov == bv && oe < be))) { bv = ov; be = oe; }
         }
-        total += bv;
-        if (lane == 0) { idx[(size_t)t * top + k] = be; wts[(size_t)t * top + k] = bv; }
-        if ((be & 31) == lane) s[be] = -1.f;
+        if (be < 0) be = k;                                            // (nothing compared: the logits are not numbers; stay inside the tables)
+        const float w = s[be];
+        total += w;
+        if (lane == 0) { idx[(size_t)t * top + k] = be; wts[(size_t)t * top + k] = w; }
+        __syncwarp();
+        if ((be & 31) == lane) c[be] = __int_as_float(0x7fc00000);
         __syncwarp();
     }
     for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= renorm ? scale / total : scale;
@@ -110,7 +130,7 @@ moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, in
 
 // one CTA.  pairs P = T * top.  tiles: int32 [max_tiles][4] = (expert, first row, rows, 0); meta[0] = number of tiles.
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows, int max_tiles, int* __restrict__ offsets,
+moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_experts, int tile_rows, int max_tiles, int* __restrict__ offsets,
                 int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos, int* __restrict__ tiles, int* __restrict__ meta) {
     __shared__ int count[MAX_EXPERTS], cursor[MAX_EXPERTS];
     TTIE_PDL_ENTRY();
@@ -122,7 +142,7 @@ moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_rows, int ma
         int at = 0, nt = 0;
         for (int e = 0; e < E; ++e) {
             offsets[e] = at; cursor[e] = at;
-            for (int r = 0; r < count[e] && nt < max_tiles; r += tile_rows, ++nt) {
+            for (int r = 0; e < tile_experts && r < count[e] && nt < max_tiles; r += tile_rows, ++nt) {
                 tiles[4 * nt] = e; tiles[4 * nt + 1] = at + r; tiles[4 * nt + 2] = min(tile_rows, count[e] - r); tiles[4 * nt + 3] = 0;
             }
             at += count[e];
@@ -299,14 +319,18 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, long long ldx, const
 
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
-                                   const T* __restrict__ shared, int T_, int d, int top, float* __restrict__ out) {
+                                   const T* __restrict__ shared, int T_, int d, int top, float* __restrict__ out,
+                                   const int* __restrict__ idx, int first_identity, const T* __restrict__ x, long long ldx) {
     TTIE_PDL_ENTRY();
     const size_t total = (size_t)T_ * d;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / d;
         const int i = (int)(e % d);
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc = fmaf(wts[t * top + k], to_f32(Y[(size_t)pos_of_pair[t * top + k] * d + i]), acc);
+        for (int k = 0; k < top; ++k) {
+            const bool same = idx && idx[t * top + k] >= first_identity;       // an identity expert: its output is the token's own row
+            acc = fmaf(wts[t * top + k], same ? to_f32(x[t * ldx + i]) : to_f32(Y[(size_t)pos_of_pair[t * top + k] * d + i]), acc);
+        }
         if (shared) acc += to_f32(shared[e]);
         out[e] = acc;
     }
@@ -314,7 +338,8 @@ __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restri
 
 // bfloat16 expert rows and shared rows, eight values per thread (d a multiple of 8)
 __global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
-                                        const __nv_bfloat16* __restrict__ shared, int T_, int d8, int top, float* __restrict__ out) {
+                                        const __nv_bfloat16* __restrict__ shared, int T_, int d8, int top, float* __restrict__ out,
+                                        const int* __restrict__ idx, int first_identity, const __nv_bfloat16* __restrict__ x, long long ldx) {
     TTIE_PDL_ENTRY();
     const size_t total = (size_t)T_ * d8;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
@@ -325,7 +350,8 @@ __global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, con
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int k = 0; k < top; ++k) {
             const float w = wts[t * top + k];
-            const uint4 v = *reinterpret_cast<const uint4*>(Y + (size_t)pos_of_pair[t * top + k] * d8 * 8 + i);
+            const bool same = idx && idx[t * top + k] >= first_identity;
+            const uint4 v = *reinterpret_cast<const uint4*>(same ? x + t * ldx + i : Y + (size_t)pos_of_pair[t * top + k] * d8 * 8 + i);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
             for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] = fmaf(w, f.x, acc[2 * j]); acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]); }
@@ -365,22 +391,24 @@ extern "C" int ttie_moe_max_experts() { return MAX_EXPERTS; }
 extern "C" int ttie_moe_tile_rows() { return BM; }
 
 extern "C" int ttie_moe_route(const float* logits, int T, int E, int groups, int keep, int group_top, int top, float scale, int renorm,
-                              int* idx, float* wts, void* stream) {
+                              int softmax, const float* correction, int* idx, float* wts, void* stream) {
     if (T <= 0) return 0;
     if (E < 1 || E > MAX_EXPERTS || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)
         || group_top < 1 || group_top > 2)
         TTIE_FAIL("moe_route: %d experts in %d groups, keep %d, group score of %d, top %d", E, groups, keep, group_top, top);
-    TTIE_LAUNCH(moe_route_kernel, ceil_div(T, ROUTE_WARPS), ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * (E + 2 * groups) * sizeof(float),
-                (cudaStream_t)stream, logits, T, E, groups, keep, group_top, top, scale, renorm, idx, wts);
+    TTIE_LAUNCH(moe_route_kernel, ceil_div(T, ROUTE_WARPS), ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * (2 * E + 2 * groups) * sizeof(float),
+                (cudaStream_t)stream, logits, T, E, groups, keep, group_top, top, scale, renorm, softmax, correction, idx, wts);
     TTIE_CHECK_LAUNCH("moe_route");
     return 0;
 }
 
-extern "C" int ttie_moe_plan(const int* idx, int P, int E, int max_tiles, int* offsets, int* pos_of_pair, int* pair_of_pos, int* tiles,
-                             int* meta, void* stream) {
+extern "C" int ttie_moe_plan(const int* idx, int P, int E, int tile_experts, int max_tiles, int* offsets, int* pos_of_pair, int* pair_of_pos,
+                             int* tiles, int* meta, void* stream) {
     if (P <= 0) return 0;
     if (E > MAX_EXPERTS) TTIE_FAIL("moe_plan: %d experts (limit %d)", E, MAX_EXPERTS);
-    TTIE_LAUNCH(moe_plan_kernel, 1, 1024, 0, (cudaStream_t)stream, idx, P, E, BM, max_tiles, offsets, pos_of_pair, pair_of_pos, tiles, meta);
+    if (tile_experts < 0 || tile_experts > E) TTIE_FAIL("moe_plan: %d of %d experts own matrices", tile_experts, E);
+    TTIE_LAUNCH(moe_plan_kernel, 1, 1024, 0, (cudaStream_t)stream, idx, P, E, tile_experts, BM, max_tiles, offsets, pos_of_pair, pair_of_pos, tiles,
+                meta);
     TTIE_CHECK_LAUNCH("moe_plan");
     return 0;
 }
@@ -430,19 +458,24 @@ extern "C" int ttie_gather_rows(const void* x, long long ldx, const int* row_of,
     return 0;
 }
 
+// idx, first_identity, x, ldx: the choices, the first identity expert and the tokens' own rows (compute dtype, row stride ldx);
+// idx null: no identity experts
 extern "C" int ttie_moe_combine(const void* Y, int y_dtype, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
-                                float* out, int dtype, void* stream) {
+                                float* out, int dtype, const int* idx, int first_identity, const void* x, long long ldx, void* stream) {
     if (T <= 0) return 0;
+    if (idx && !x) TTIE_FAIL("moe_combine: identity experts need the tokens' own rows");
     const size_t total = (size_t)T * d;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == kBF16 && y_dtype == kBF16 && d % 8 == 0 && ((((uintptr_t)Y) | ((uintptr_t)shared) | ((uintptr_t)out)) & 15) == 0) {
-        TTIE_LAUNCH(moe_combine_vec8_kernel, grid_for(total / 8), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d / 8, top, out);
+    if (dtype == kBF16 && y_dtype == kBF16 && d % 8 == 0 && ((((uintptr_t)Y) | ((uintptr_t)shared) | ((uintptr_t)out)) & 15) == 0
+        && !(idx && ((((uintptr_t)x) & 15) || ldx % 8))) {
+        TTIE_LAUNCH(moe_combine_vec8_kernel, grid_for(total / 8), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d / 8, top, out,
+                    idx, first_identity, (const __nv_bfloat16*)x, ldx);
         TTIE_CHECK_LAUNCH("moe_combine");
         return 0;
     }
-    if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out);
-    else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
-    else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out);
+    if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out, idx, first_identity, (const float*)x, ldx);
+    else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx);
+    else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx);
     else TTIE_FAIL("moe_combine: expert rows of dtype %d beside a shared expert of dtype %d", y_dtype, dtype);
     TTIE_CHECK_LAUNCH("moe_combine");
     return 0;

@@ -35,7 +35,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page (must divide 64)")
-    ap.add_argument("--max-live", type=int, default=8, help="state slots (requests live at a time)")
+    ap.add_argument("--max-live", type=int, default=4, help="state slots (requests live at a time)")
     ap.add_argument("--device", default="cuda:0")
     return ap
 

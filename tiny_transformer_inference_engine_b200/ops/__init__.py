@@ -25,7 +25,7 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 _c_int, _c_ll, _c_float, _c_void = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
 
 _SIGNATURES = {
-    "ttie_embed": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_embed": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ttie_add_rmsnorm": [_c_void, _c_void, _c_void, _c_int, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int,
                          _c_float, _c_int, _c_void],
     "ttie_rope_store_partial": [_c_void, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int,
@@ -42,16 +42,16 @@ _SIGNATURES = {
                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_paged_attention": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
                              _c_void, _c_int, _c_void],
     "ttie_paged_attention_mma": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
                                  _c_void, _c_void],
     "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int,
+                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
-                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int,
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_tc_pair": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
@@ -69,18 +69,18 @@ _SIGNATURES = {
                         _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void, _c_int, _c_void,
                         _c_int, _c_void],
     "ttie_glu": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void],
-    "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_void, _c_void],
-    "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
+    "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
+    "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
     "ttie_skinny_gemm_glu": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
     "ttie_gather_rows": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
-    "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int, _c_void, _c_ll, _c_void],
     "ttie_qkv_conv_rope_store": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void,
-                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
-                                 _c_int, _c_int, _c_int, _c_void],
+                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_float, _c_int, _c_float, _c_int,
+                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_conv_tail_update": [_c_void, _c_ll, _c_int, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
-    "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_token_shift_mix": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int,
                              _c_void],
     "ttie_wkv_decay": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_void],
@@ -90,6 +90,9 @@ _SIGNATURES = {
                          _c_void],
     "ttie_mlstm_scan": [_c_void, _c_void, _c_void, _c_ll, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int,
                         _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ttie_rotate_heads": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_float, _c_void, _c_int, _c_void],
+    "ttie_retention_scan": [_c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int,
+                            _c_int, _c_int, _c_int, _c_void],
     "ttie_head_norm_gate": [_c_void, _c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_int, _c_void],
     "ttie_activation": [_c_void, _c_void, _c_ll, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ttie_matrix_state_pad": [_c_int],
@@ -223,20 +226,23 @@ class CudaOps:
             raise KernelError(f"rmsnorm: width {dim} needs {dim * 4} bytes of shared memory (limit 204800)")
 
     # ------------------------------------------------------------------ ops
-    def embed(self, token_ids, table, out):
+    def embed(self, token_ids, table, out, scale=1.0):
+        """out[t] = table[token_ids[t]] * scale (float32)."""
         T, d = out.shape
-        self._check(self.lib.ttie_embed(_ptr(token_ids), _ptr(table), _ptr(out), T, d, table.shape[0],
+        self._check(self.lib.ttie_embed(_ptr(token_ids), _ptr(table), _ptr(out), T, d, table.shape[0], float(scale),
                                         self._dt(table), self._stream(out)), "embed")
         self.launches += 1
 
     @staticmethod
     def _delta_args(delta):
         """(delta pointer, partial pointer, S, stride) for a delta that is None, [T, d] in the compute
-        dtype, or float32 partial sums [S, T, d]."""
+        dtype, float32 [T, d], or float32 partial sums [S, T, d]."""
         if delta is None:
             return None, None, 0, 0
         if delta.dim() == 3:
             return None, delta.data_ptr(), delta.shape[0], delta.stride(0)
+        if delta.dtype == torch.float32:                     # one 32-bit sum [T, d], whatever the compute dtype
+            return None, delta.data_ptr(), 1, 0
         return delta.data_ptr(), None, 0, 0
 
     def add_rmsnorm(self, resid, delta, weight, eps, out):
@@ -792,10 +798,13 @@ class CudaOps:
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
                         query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out,
-                        plan=None, softcap=0.0):
+                        plan=None, softcap=0.0, chunk=0):
         """Causal attention of the step's query rows over the paged keys and values.  ``window`` > 0: a row at position p
-        sees keys p - window + 1 .. p.  ``softcap`` > 0: a score s (scale applied) becomes softcap * tanh(s / softcap)
-        before mask and softmax."""
+        sees keys p - window + 1 .. p.  ``chunk`` > 0 (instead of a window): a row at position p sees the keys of its own
+        chunk of ``chunk`` positions up to p, chunks counted from position 0 of the sequence.  ``softcap`` > 0: a score s
+        (scale applied) becomes softcap * tanh(s / softcap) before mask and softmax."""
+        if chunk and window:
+            raise KernelError("paged_attention: a window and a chunk size exclude each other")
         T = qkv.shape[0]
         if max_kv_len > block_table.shape[1] * page_size:
             raise KernelError(f"paged_attention: a block table of {block_table.shape[1]} pages of {page_size} keys cannot cover {max_kv_len} keys")
@@ -808,7 +817,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention_tc(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
-                num_kv_heads, head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
+                num_kv_heads, head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
                 1 if kernel == "tcpp" else 0, self._stream(qkv)), "paged_attention_tc")
             self.launches += 2 if num_splits > 1 else 1
             return
@@ -820,7 +829,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention_mma_form(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
-                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
+                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
                 form, self._stream(qkv)), "paged_attention_mma")
             self.launches += 2 if (num_splits > 1 and not form) else 1
             return
@@ -828,7 +837,7 @@ class CudaOps:
             self._check(self.lib.ttie_paged_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
-                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), num_splits, split_len, _ptr(scratch),
+                head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
                 self._dt(qkv), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
 
@@ -943,19 +952,26 @@ class CudaOps:
 
     # ---- attention with a short convolution on its projections, partial rotation, another value size, gated heads
     def qkv_conv_rope_store(self, proj, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, taps, conv_w, tail, positions, token_seq,
-                            query_start_loc, slot_ids, cs_table, rot, style, k_pages, v_pages, block_table, page_size, write_kv):
+                            query_start_loc, slot_ids, cs_table, rot, style, k_pages, v_pages, block_table, page_size, write_kv,
+                            norm_w=None, norm_eps=0.0, v_from_k=False, q_temp=None):
         """From a step's projected rows ``proj`` [T, >= Hq*D + Hkv*D + Hkv*Dv] (columns [q | k | v]): the short causal
         convolution over time (``conv_w`` float32 tap-major [taps, channels]; ``tail`` float32 state rows
         [slots + 1, taps - 1, channels] with each request's last projected rows; ``taps`` 1 and ``conv_w`` None: none), the
         rotation of the first ``rot`` values of every q and k head (``style`` 0: pairs (2i, 2i+1), 1: pairs (i, i + rot/2);
         ``cs_table`` from ``rope_table``), and the store of k and v into the pages, rows padded with zeros to
-        ``padded_dim``.  Returns q [T, Hq * padded_dim].  The state rows are advanced by ``conv_tail_update``."""
+        ``padded_dim``.  ``norm_w`` (float32 [2, head_dim]: the query heads' weights, then the key heads'): every q and k head
+        is divided by its root mean square (``norm_eps`` inside the root) and multiplied by its weights, before the rotation.
+        ``v_from_k``: ``proj`` has no v columns and a value head is its key head as it stands before norm and rotation.
+        ``q_temp`` (coef, every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+        Returns q [T, Hq * padded_dim].  The state rows are advanced by ``conv_tail_update``."""
         T = proj.shape[0]
         q = torch.empty((T, num_heads * padded_dim), dtype=proj.dtype, device=proj.device)
         self._check(self.lib.ttie_qkv_conv_rope_store(
             _ptr(proj), proj.stride(0), T, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, int(taps), _ptr(conv_w), _ptr(tail),
             0 if tail is None else tail.shape[0], _ptr(positions), _ptr(token_seq), _ptr(query_start_loc), _ptr(slot_ids),
-            _ptr(cs_table), int(rot), int(style), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+            _ptr(cs_table), int(rot), int(style), _ptr(norm_w), float(norm_eps), 1 if v_from_k else 0,
+            float(q_temp[0]) if q_temp else 0.0, int(q_temp[1]) if q_temp else 0,
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             int(page_size), k_pages.shape[0], 1 if write_kv else 0, self._dt(proj), self._stream(proj)), "qkv_conv_rope_store")
         self.launches += 1
         return q
@@ -969,12 +985,12 @@ class CudaOps:
                                                    self._stream(proj)), "conv_tail_update")
         self.launches += 1
 
-    def gate_head_rows(self, attn, gate, num_heads, v_dim, padded_dim):
+    def gate_head_rows(self, attn, gate, num_heads, v_dim, padded_dim, per_value=False):
         """out[t, h, :v_dim] = attn[t, h, :v_dim] * sigmoid(gate[t, h]); attn [T, H * padded_dim], gate a view [T, H] with a row
-        stride, or None (then only the padding is dropped)."""
+        stride, or None (then only the padding is dropped).  ``per_value``: gate is [T, H * v_dim], one number per value."""
         T = attn.shape[0]
         out = torch.empty((T, num_heads * v_dim), dtype=attn.dtype, device=attn.device)
-        self._check(self.lib.ttie_gate_head_rows(_ptr(attn), _ptr(gate), 0 if gate is None else gate.stride(0), T, num_heads, v_dim,
+        self._check(self.lib.ttie_gate_head_rows(_ptr(attn), _ptr(gate), 0 if gate is None else gate.stride(0), 1 if per_value else 0, T, num_heads, v_dim,
                                                  padded_dim, _ptr(out), self._dt(attn), self._stream(attn)), "gate_head_rows")
         self.launches += 1
         return out
@@ -1055,9 +1071,35 @@ class CudaOps:
         self.launches += 1
         return out
 
+    def rotate_heads(self, src, heads, dim, cs_table, rot, style, scale_from=None, scale=1.0):
+        """float32 [T, heads * dim]: the ``heads`` head rows of ``dim`` values at the start of every row of ``src`` (a view with a
+        row stride), the first ``rot`` values of each rotated at the token's position (``cs_table`` from ``rope_table``;
+        ``style`` 0: pairs (2i, 2i+1), 1: pairs (i, i + rot/2)), and the heads from ``scale_from`` on multiplied by ``scale``."""
+        T = src.shape[0]
+        out = torch.empty((T, heads * dim), dtype=torch.float32, device=src.device)
+        self._check(self.lib.ttie_rotate_heads(_ptr(src), src.stride(0), T, int(heads), int(dim), int(rot), int(style), _ptr(cs_table),
+                                               heads if scale_from is None else int(scale_from), float(scale), _ptr(out), self._dt(src),
+                                               self._stream(src)), "rotate_heads")
+        self.launches += 1
+        return out
+
+    def retention_scan(self, q, k, v, decay, S, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim):
+        """Retention's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim] (advanced in
+        place): S <- decay_h S + k v^T, o = S^T q.  q, k float32 [T, H*dim] views with one row stride; v [T, H*v_dim] in the
+        compute dtype, a view with a row stride; ``decay`` float32 [H].  Returns o float32 [T, H*v_dim]."""
+        T = q.shape[0]
+        out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
+        if q.stride(0) != k.stride(0) or q.dtype != torch.float32 or k.dtype != torch.float32:
+            raise KernelError("retention_scan: q and k must be float32 and share a row stride")
+        self._check(self.lib.ttie_retention_scan(_ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(decay), _ptr(S), S.shape[0],
+                                                 _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads, dim, v_dim,
+                                                 self._dt(v), self._stream(q)), "retention_scan")
+        self.launches += 1
+        return out
+
     def head_norm_gate(self, o, gate, weight, num_heads, v_dim, eps, act):
         """out = o / rms(o over each head) * weight * act(gate); o float32 [T, H*v_dim], gate a view [T, H*v_dim] with a row
-        stride, weight float32 [H*v_dim]; ``act``: "silu" or "sigmoid".  Returns the compute dtype of ``gate``."""
+        stride, weight float32 [H*v_dim] or None (no weight); ``act``: "silu" or "sigmoid".  Returns the compute dtype of ``gate``."""
         T = o.shape[0]
         out = torch.empty((T, num_heads * v_dim), dtype=gate.dtype, device=o.device)
         self._check(self.lib.ttie_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), T, num_heads, v_dim, float(eps),
@@ -1102,27 +1144,30 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def moe_route(self, logits, groups, keep, group_top, top, scale, renorm=False):
-        """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E]."""
+    def moe_route(self, logits, groups, keep, group_top, top, scale, renorm=False, score="sigmoid", correction=None):
+        """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E].  ``score``: "sigmoid" per
+        expert or "softmax" over all of them; ``correction`` float32 [E]: added to the scores for the choice only."""
         T, E = logits.shape
         idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
         wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
         self._check(self.lib.ttie_moe_route(_ptr(logits), T, E, groups, keep, group_top, top, float(scale), 1 if renorm else 0,
-                                            _ptr(idx), _ptr(wts), self._stream(logits)), "moe_route")
+                                            {"sigmoid": 0, "softmax": 1}[score], _ptr(correction), _ptr(idx), _ptr(wts),
+                                            self._stream(logits)), "moe_route")
         self.launches += 1
         return idx, wts
 
-    def moe_plan(self, idx, num_experts):
+    def moe_plan(self, idx, num_experts, identity=0):
         """Sorts the (token, choice) pairs by expert on the device: a dict with ``pos_of_pair``, ``pair_of_pos``, ``offsets``,
-        the row-tile table and its size bound."""
+        the row-tile table and its size bound.  The last ``identity`` of the ``num_experts`` own no matrices: their pairs are
+        sorted behind the others and get no row tiles."""
         P = idx.numel()
         tile = int(self.lib.ttie_moe_tile_rows())
         max_tiles = P // tile + num_experts
         buf = torch.empty(2 * P + num_experts + 1 + 4 * max_tiles + 4, dtype=torch.int32, device=idx.device)
         plan = {"pos_of_pair": buf[:P], "pair_of_pos": buf[P:2 * P], "offsets": buf[2 * P:2 * P + num_experts + 1],
                 "tiles": buf[2 * P + num_experts + 1:2 * P + num_experts + 1 + 4 * max_tiles], "meta": buf[-4:], "max_tiles": max_tiles,
-                "pairs": P}
-        self._check(self.lib.ttie_moe_plan(_ptr(idx), P, num_experts, max_tiles, _ptr(plan["offsets"]), _ptr(plan["pos_of_pair"]),
+                "pairs": P, "idx": idx, "real_experts": num_experts - int(identity)}
+        self._check(self.lib.ttie_moe_plan(_ptr(idx), P, num_experts, num_experts - int(identity), max_tiles, _ptr(plan["offsets"]), _ptr(plan["pos_of_pair"]),
                                            _ptr(plan["pair_of_pos"]), _ptr(plan["tiles"]), _ptr(plan["meta"]), self._stream(idx)),
                     "moe_plan")
         self.launches += 1
@@ -1146,7 +1191,7 @@ class CudaOps:
                                                   x.shape[1], _ptr(rows), self._dt(x), self._stream(x)), "gather_rows")
             self.launches += 1
         try:
-            return self._grouped_mm(rows, w.transpose(1, 2), offs=plan["offsets"][1:])
+            return self._grouped_mm(rows, w.transpose(1, 2), offs=plan["offsets"][1:w.shape[0] + 1])
         except (RuntimeError, TypeError, NotImplementedError):
             if torch.cuda.is_current_stream_capturing():
                 raise
@@ -1203,13 +1248,19 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def moe_combine(self, y, plan, wts, shared, num_tokens, dim):
-        """float32 [T, d]: the weighted sum of each token's expert rows (+ the shared expert's output)."""
+    def moe_combine(self, y, plan, wts, shared, num_tokens, dim, x=None):
+        """float32 [T, d]: the weighted sum of each token's expert rows (+ the shared expert's output).  ``x`` [T, d] (compute
+        dtype): the tokens' own rows, which an identity expert returns (a plan made with ``identity`` > 0 needs them)."""
         out = torch.empty((num_tokens, dim), dtype=torch.float32, device=y.device)
         top = wts.shape[1]
-        sdt = self._dt(shared) if shared is not None else self._dt(y)
+        sdt = self._dt(shared) if shared is not None else self._dt(x) if x is not None else self._dt(y)
+        identity = plan["real_experts"] < plan["offsets"].numel() - 1
+        if identity and x is None:
+            raise KernelError("moe_combine: identity experts return the tokens' own rows, which were not given")
         self._check(self.lib.ttie_moe_combine(_ptr(y), self._dt(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim,
-                                              top, _ptr(out), sdt, self._stream(y)), "moe_combine")
+                                              top, _ptr(out), sdt, _ptr(plan["idx"]) if identity else None, plan["real_experts"],
+                                              _ptr(x) if identity else None, x.stride(0) if identity else 0, self._stream(y)),
+                    "moe_combine")
         self.launches += 1
         return out
 

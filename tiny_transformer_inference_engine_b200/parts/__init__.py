@@ -2,4 +2,4 @@
 from .base import (PartSpec, ParamSpec, LayerSpec, RunEntry, ModelSpec, PagedKVNeed, FixedStateNeed,
                    PagedKVView, FixedStateView, StepContext, ResidualStream, Part, Norm, PositionEncoding,
                    Mixer, FeedForward, Embedding, Head, Block)
-from . import norm, rope, attention, latent_attention, rglru, wkv, mlstm, ffn, moe, embedding, block  # noqa: F401  (registration)
+from . import norm, rope, attention, latent_attention, rglru, wkv, mlstm, retention, ffn, moe, embedding, block  # noqa: F401  (registration)

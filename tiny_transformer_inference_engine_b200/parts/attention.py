@@ -9,9 +9,10 @@ project the concatenated heads with ``out``.  Query head ``h`` uses kv head
 ``h // (heads / kv_heads)`` (kernels/flashattn/flashattn.cu, same rule).
 
 The three projections are fused at load into one matrix ``[(Hq+2*Hkv)*D, d]`` so one
-product feeds the rotate-and-store kernel.  ``window`` (keys ``pos-window+1..pos``)
+product feeds the rotate-and-store kernel.  ``window`` (keys ``pos-window+1..pos``), ``chunk`` (instead of a
+window: a token sees the keys of its own chunk of ``chunk`` positions, chunks counted from position 0 of the sequence)
 and ``page_size`` (a page size of this layer's own cache group) are parameters of the part; the reference's
-model has neither.  A run entry that reads
+model has none of them.  A run entry that reads
 another entry's cache (``shares_kv``) has no k/v projection and stores nothing.
 
 Further options, each with its constants as parameters (any of them selects the general step below):
@@ -19,9 +20,14 @@ Further options, each with its constants as parameters (any of them selects the 
 channel of q, k and v, directly behind the projection and before the rotation; weights ``<name><conv_suffix>``
 [channels, taps], tap ``taps - 1`` multiplies the current token; the last ``taps - 1`` projected rows of a request are
 kept in a state row), a position encoding that rotates only the first ``position.dim`` values of a head, ``softcap``
-(a score s becomes ``softcap * tanh(s / softcap)`` before mask and softmax), ``gated`` (head h's output is scaled by
-``sigmoid(W_g x)_h``, one number per head), ``qkv_bias`` (biases on q, k and v only).  The general step: one product
-``[W_q; W_k; W_v; W_g] x``; one kernel convolves, rotates, writes q and stores k and v - rows padded with zeros to
+(a score s becomes ``softcap * tanh(s / softcap)`` before mask and softmax), ``gated`` (``True`` or ``"head"``: head h's
+output is scaled by ``sigmoid(W_g x)_h``, one number per head; ``"value"``: the concatenated heads are multiplied value by
+value with ``sigmoid(W_g x)``, ``W_g`` as large as ``W_q`` would be at the value size), ``qkv_bias`` (biases on q, k and v
+only), ``qk_norm`` (its eps: every query and key head is divided by its root mean square and multiplied by a weight of
+``head_dim`` values that all heads share, ``<q><norm_suffix>`` and ``<k><norm_suffix>``, before the rotation), ``v_from_k``
+(there is no value projection: a value head is its key head as projected, before norm and rotation), ``q_temp``
+(``coef``, ``every``: the query at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``).  The general step: one product
+``[W_q; W_k; W_v; W_g] x``; one kernel convolves, normalises, rotates, writes q and stores k and v - rows padded with zeros to
 ``padded_dim``, a multiple of 16 that holds both sizes, so every attention kernel of the package applies; a second moves the
 convolution's inputs into the state row; attention; the gate kernel drops the padding; ``W_o``.
 """
@@ -43,15 +49,21 @@ class PagedAttention(Mixer):
                  scale: Optional[float] = None, shares_kv: bool = False,
                  names: Optional[Dict[str, str]] = None, page_size: Optional[int] = None,
                  v_head_dim: Optional[int] = None, conv_taps: Optional[int] = None, softcap: Optional[float] = None,
-                 gated: bool = False, qkv_bias: bool = False, weight_suffix: str = ".weight", bias_suffix: str = ".bias",
-                 conv_suffix: str = ".conv"):
+                 gated=False, qkv_bias: bool = False, weight_suffix: str = ".weight", bias_suffix: str = ".bias",
+                 conv_suffix: str = ".conv", chunk: Optional[int] = None, qk_norm: Optional[float] = None,
+                 norm_suffix: str = ".norm", v_from_k: bool = False, q_temp: Optional[Dict[str, float]] = None):
         super().__init__(prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         if window is not None and window < 1:
             raise ValueError(f"window must be >= 1 or None, got {window}")
+        if chunk is not None and (chunk < 1 or window is not None):
+            raise ValueError(f"chunk must be >= 1 or None and excludes a window, got chunk={chunk} window={window}")
+        if gated not in (False, True, "head", "value"):
+            raise ValueError(f"gated must be False, True / 'head' or 'value', got {gated!r}")
         self.d_model, self.num_heads, self.num_kv_heads, self.head_dim = d_model, num_heads, num_kv_heads, head_dim
         self.bias, self.window, self.shares_kv = bool(bias), window, bool(shares_kv)
+        self.chunk = None if chunk is None else int(chunk)
         self.page_size = None if page_size is None else int(page_size)     # None: the engine's page size
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.position = build_part("position", position)
@@ -68,17 +80,28 @@ class PagedAttention(Mixer):
         if self.softcap is not None and self.softcap <= 0:
             raise ValueError(f"softcap must be positive or None, got {softcap}")
         self.gated, self.qkv_bias = bool(gated), bool(qkv_bias)
-        self.weight_suffix, self.bias_suffix, self.conv_suffix = weight_suffix, bias_suffix, conv_suffix
+        self.gate_per_value = gated == "value"
+        self.weight_suffix, self.bias_suffix, self.conv_suffix, self.norm_suffix = weight_suffix, bias_suffix, conv_suffix, norm_suffix
+        self.qk_norm = None if qk_norm is None else float(qk_norm)
+        self.v_from_k = bool(v_from_k)
+        if self.v_from_k and self.v_head_dim != head_dim:
+            raise ValueError(f"values that are the keys have the keys' size {head_dim}, not {self.v_head_dim}")
+        self.q_temp = None
+        if q_temp is not None:
+            self.q_temp = (float(q_temp["coef"]), int(q_temp["every"]))
+            if self.q_temp[1] < 1:
+                raise ValueError(f"q_temp.every must be >= 1, got {q_temp['every']}")
         self.rot_dim = int(getattr(self.position, "dim", 0) or 0)      # rotated values per head (0: none)
         if self.rot_dim > head_dim:
             raise ValueError(f"the position encoding rotates {self.rot_dim} values of a head of {head_dim}")
         self.general = (self.v_head_dim != head_dim or self.has_conv or self.gated or self.qkv_bias
-                        or self.rot_dim not in (0, head_dim))
+                        or self.rot_dim not in (0, head_dim) or self.qk_norm is not None or self.v_from_k
+                        or self.q_temp is not None)
         if self.general and (self.shares_kv or self.bias):
             raise ValueError("the general attention step has neither a shared cache nor an output bias")
         self.padded_dim = -(-max(head_dim, self.v_head_dim) // 16) * 16 if self.general else head_dim
-        self.channels = (num_heads + num_kv_heads) * head_dim + num_kv_heads * self.v_head_dim      # of [q | k | v]
-        self.conv_w = None
+        self.channels = (num_heads + num_kv_heads) * head_dim + (0 if self.v_from_k else num_kv_heads * self.v_head_dim)   # of [q | k | v]
+        self.conv_w = self.norm_w = None
 
     def children(self):
         return [self.position]
@@ -102,6 +125,8 @@ class PagedAttention(Mixer):
     def _general_specs(self):
         n, d, D, Dv, ws = self.names, self.d_model, self.head_dim, self.v_head_dim, self.weight_suffix
         rows = {"q": self.num_heads * D, "k": self.num_kv_heads * D, "v": self.num_kv_heads * Dv}
+        if self.v_from_k:
+            del rows["v"]
         specs = {f"{n['o']}{ws}": ParamSpec((d, self.num_heads * Dv))}
         for key, r in rows.items():
             specs[f"{n[key]}{ws}"] = ParamSpec((r, d))
@@ -109,23 +134,29 @@ class PagedAttention(Mixer):
                 specs[f"{n[key]}{self.bias_suffix}"] = ParamSpec((r,), storage="vector", init="normal")
             if self.has_conv:
                 specs[f"{n[key]}{self.conv_suffix}"] = ParamSpec((r, self.conv_taps), storage="vector", init="normal", std=0.5)
+        if self.qk_norm is not None:
+            for key in ("q", "k"):
+                specs[f"{n[key]}{self.norm_suffix}"] = ParamSpec((D,), storage="vector", init="ones")
         if self.gated:
-            specs[f"{n['g']}{ws}"] = ParamSpec((self.num_heads, d))
+            specs[f"{n['g']}{ws}"] = ParamSpec((self.num_heads * (Dv if self.gate_per_value else 1), d))
         return specs
 
     def _general_load(self, params):
         n, ws = self.names, self.weight_suffix
-        keys = ["q", "k", "v"] + (["g"] if self.gated else [])
+        qkv = ["q", "k"] if self.v_from_k else ["q", "k", "v"]
+        keys = qkv + (["g"] if self.gated else [])
         self.w_in = torch.cat([params[f"{n[k]}{ws}"] for k in keys], dim=0).contiguous()
         self.w_out = params[f"{n['o']}{ws}"].contiguous()
         if self.qkv_bias:
-            b = [params[f"{n[k]}{self.bias_suffix}"].to(self.w_in.dtype) for k in ("q", "k", "v")]
+            b = [params[f"{n[k]}{self.bias_suffix}"].to(self.w_in.dtype) for k in qkv]
             if self.gated:
-                b.append(torch.zeros(self.num_heads, dtype=self.w_in.dtype, device=self.w_in.device))
+                b.append(torch.zeros(self.w_in.shape[0] - self.channels, dtype=self.w_in.dtype, device=self.w_in.device))
             self.b_in = torch.cat(b, dim=0).contiguous()
         if self.has_conv:                                               # tap-major, 32-bit: a tap's weights lie side by side
-            w = torch.cat([params[f"{n[k]}{self.conv_suffix}"].float() for k in ("q", "k", "v")], dim=0)
+            w = torch.cat([params[f"{n[k]}{self.conv_suffix}"].float() for k in qkv], dim=0)
             self.conv_w = w.t().contiguous()
+        if self.qk_norm is not None:                                    # 32-bit, the query heads' weights then the key heads'
+            self.norm_w = torch.stack([params[f"{n[k]}{self.norm_suffix}"].float() for k in ("q", "k")]).contiguous()
 
     def load(self, params):
         if self.general:
@@ -148,7 +179,7 @@ class PagedAttention(Mixer):
 
     # ---------------------------------------------------------------- cache
     def cache_needs(self):
-        needs = [PagedKVNeed(self.num_kv_heads, self.padded_dim, self.window, self.page_size)]
+        needs = [PagedKVNeed(self.num_kv_heads, self.padded_dim, self.window, self.page_size, chunk=self.chunk)]
         if self.conv_taps > 1:
             needs.append(FixedStateNeed((self.conv_taps - 1, self.channels), "float32"))
         return needs
@@ -166,13 +197,14 @@ class PagedAttention(Mixer):
         state = tail.state if tail is not None else None
         q = ops.qkv_conv_rope_store(proj, Hq, Hkv, D, Dv, Dp, self.conv_taps, self.conv_w, state, ctx.positions, ctx.token_seq,
                                     ctx.query_start_loc, ctx.slot_ids, cs, rot, style, cache.k_pages, cache.v_pages,
-                                    cache.block_table, cache.page_size, cache.writable)
+                                    cache.block_table, cache.page_size, cache.writable, norm_w=self.norm_w,
+                                    norm_eps=self.qk_norm or 0.0, v_from_k=self.v_from_k, q_temp=self.q_temp)
         if self.conv_taps > 1 and tail.writable:
             ops.conv_tail_update(proj, C, self.conv_taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
         out = torch.empty((T, Hq * Dp), dtype=x.dtype, device=x.device)
         self._attend(q, Dp, ctx, cache, out)
         if self.gated or Dp != Dv:
-            out = ops.gate_head_rows(out, proj[:, C:] if self.gated else None, Hq, Dv, Dp)
+            out = ops.gate_head_rows(out, proj[:, C:] if self.gated else None, Hq, Dv, Dp, per_value=self.gate_per_value)
         return ops.linear(out, self.w_out, None, partial_ok=True)
 
     def _attend(self, q, D, ctx, cache, out):
@@ -183,7 +215,7 @@ class PagedAttention(Mixer):
             c = classes[0]
             ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
                                 c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
-                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0)
+                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0, chunk=self.chunk or 0)
             return
         for ci, c in enumerate(classes):
             key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
@@ -192,7 +224,8 @@ class PagedAttention(Mixer):
                 views = ctx.step_cache[key] = (cache.block_table[c.seq_lo:c.seq_hi], ctx.seq_lens[c.seq_lo:c.seq_hi])
             ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
                                 cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
-                                c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi], softcap=self.softcap or 0.0)
+                                c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi], softcap=self.softcap or 0.0,
+                                chunk=self.chunk or 0)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         tail = None

@@ -86,12 +86,14 @@ class ModelSpec:
 # --------------------------------------------------------------------------- cache needs
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values of every past token (or of the last ``window`` tokens) in pages."""
+    """Keys and values of every past token (or of the last ``window`` tokens, or of the current chunk of ``chunk``
+    positions) in pages."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None       # None: all keys
     page_size: Optional[int] = None    # None: the engine's page size
     planes: int = 2                    # 2: keys and values; 1: one array that is both (latent attention), handed out as K and as V
+    chunk: Optional[int] = None        # a token reads only keys of its own chunk (chunks counted from position 0); excludes window
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,7 @@
 """Token embedding and output head.
 
-Embedding (models/embedding.py:9-15): a row gather, no scale, no position term; the
-gathered row starts the 32-bit residual sum.  Head (models/transformer_block.py:170,181):
+Embedding (models/embedding.py:9-15): a row gather, no position term; the gathered row
+(times ``scale``, a parameter; the reference has none) starts the 32-bit residual sum.  Head (models/transformer_block.py:170,181):
 ``logits = x @ W.T`` without bias, untied from the embedding; logits leave in 32-bit.
 """
 from __future__ import annotations
@@ -14,9 +14,9 @@ from ..registry import register_part
 
 @register_part("embedding", "token")
 class TokenEmbedding(Embedding):
-    def __init__(self, prefix: str, vocab_size: int, dim: int, name: str = "weight"):
+    def __init__(self, prefix: str, vocab_size: int, dim: int, name: str = "weight", scale: float = 1.0):
         super().__init__(prefix)
-        self.vocab_size, self.dim, self.name = int(vocab_size), int(dim), name
+        self.vocab_size, self.dim, self.name, self.scale = int(vocab_size), int(dim), name, float(scale)
         self.table = None
 
     def param_specs(self):
@@ -27,7 +27,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         resid = torch.empty((ctx.num_tokens, self.dim), dtype=torch.float32, device=ctx.device)
-        self.ops.embed(ctx.token_ids, self.table, resid)
+        self.ops.embed(ctx.token_ids, self.table, resid, self.scale)
         return resid
 
 
