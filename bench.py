@@ -305,7 +305,33 @@ def mizupel_config(width, heads, layers=4):
             "max_seq_len": 4096}
 
 
-DESIGNS = {"munevik": ("Munevik", munevik_config, 1024), "mizupel": ("Mizupel", mizupel_config, 1024)}     # name, configuration, window
+def mokalorn_config(width, heads, layers=4):
+    """A Mokalorn model at layer sizes that resemble a real model's: grouped-query attention with heads of 128 (eight query heads
+    per kv head), the keys as values, 64 rotated values and chunks of 1,024 positions; a second attention with a value projection,
+    one kv head per eight heads and a query temperature; retention with width / 128 heads of 128 key and 128 value channels;
+    feed-forwards of 16 experts of width / 2 and two identity experts, four chosen.  Layer order: chunked attention, retention,
+    causal attention, retention, repeated."""
+    rot = {"base": 10000.0, "dims": 64}
+    att = {"heads": heads, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "mask": {"size": 1024}, "rot": rot, "scale": 128 ** -0.5}
+    att2 = {"heads": heads, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "q_temp": {"coef": 0.1, "every": 512}, "scale": 128 ** -0.5}
+    ret = {"heads": heads, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 128},
+           "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(1, heads - 1)) for i in range(heads)]}
+    moe = {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0}, "router": {"experts": 16, "identity": 2, "top": 4}}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            out.append({"type": "attention", "mixer": dict(att), "mlp": moe})
+        elif k == 2:
+            out.append({"type": "attention_2", "mixer": dict(att2), "mlp": moe})
+        else:
+            out.append({"type": "retention", "mixer": dict(ret), "mlp": moe})
+    return {"architecture": "Mokalorn", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_softcap": 30.0, "layers": out, "max_seq_len": 4096}
+
+
+DESIGNS = {"munevik": ("Munevik", munevik_config, 1024), "mizupel": ("Mizupel", mizupel_config, 1024),
+           "mokalorn": ("Mokalorn", mokalorn_config, 0)}     # name, configuration, window
 
 
 def like_config(width, heads, layers=4):
@@ -321,7 +347,7 @@ class OpRecorder:
              "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
              "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine",
              "qkv_conv_rope_store", "conv_tail_update", "gate_head_rows", "token_shift_mix", "wkv_scan", "mlstm_scan", "head_norm_gate",
-             "activation", "linear_act", "wkv_decay", "mlstm_gates")
+             "activation", "linear_act", "wkv_decay", "mlstm_gates", "rotate_heads", "retention_scan")
 
     def __init__(self, ops):
         self.ops, self.calls, self.orig, self.depth = ops, [], {}, 0
@@ -376,6 +402,12 @@ def op_cost(name, args, kw, out, kv_lens, window):
             T, per_tok, fma = q.shape[0], (2 * H * D + H * Dv) * q.element_size() + 4 * H * Dv + 8 * H, 4 * H * D * Dv
         row = state[0].numel() * 4
         return T * per_tok + 2 * n * row, ("fp32", 2 * T * fma)
+    if name == "retention_scan":                                   # like the other matrix-state scans: two multiply-adds per state element and token
+        q, v, state, n, H, D, Dv = args[0], args[2], args[4], args[7], args[8], args[9], args[10]
+        T = q.shape[0]
+        return T * (2 * H * D * 4 + H * Dv * v.element_size() + 4 * H * Dv) + 2 * n * state[0].numel() * 4, ("fp32", 2 * T * 2 * H * D * Dv)
+    if name == "rotate_heads":                                     # (src, heads, dim, ...): the rotated columns read, 32-bit rows written
+        return args[0].shape[0] * args[1] * args[2] * args[0].element_size() + _tensor_bytes(out), 0
     if name == "qkv_conv_rope_store":                              # pages and state rows are pools: count the rows read and written
         return 2 * _tensor_bytes(args[0]) + _tensor_bytes(out), 0
     if name == "conv_tail_update":                                 # (proj, channels, taps, tail, qsl, slots, requests)
@@ -400,9 +432,15 @@ def op_cost(name, args, kw, out, kv_lens, window):
     if name == "paged_attention":
         q, H, Hkv, D, kp, vp = args[0], args[1], args[2], args[3], args[4], args[5]
         planes = 1 if kp.data_ptr() == vp.data_ptr() else 2
-        vis = [min(L, window + n) if window else L for L, n in kv_lens]
+        chunk = kw.get("chunk") or 0
+        if chunk:                                                   # a token sees the keys of its own chunk up to itself
+            seen = [[p % chunk + 1 for p in range(L - n, L)] for L, n in kv_lens]
+            vis = [min(L, n + (L - n) % chunk) for L, n in kv_lens]
+            fl = sum(4 * H * D * sum(s) for s in seen)
+        else:
+            vis = [min(L, window + n) if window else L for L, n in kv_lens]
+            fl = sum(4 * H * D * n * (min(L, window) if window else (L - n / 2)) for L, n in kv_lens)
         kv_bytes = sum(vis) * Hkv * D * kp.element_size() * planes
-        fl = sum(4 * H * D * n * (min(L, window) if window else (L - n / 2)) for L, n in kv_lens)
         return 2 * q.shape[0] * H * D * q.element_size() + kv_bytes, fl
     if name in ("rope_store", "latent_store"):
         x = args[0]
@@ -520,7 +558,7 @@ def run_design(args, pk):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=("munevik", "mizupel"), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
+    ap.add_argument("--design", default=None, choices=("munevik", "mizupel", "mokalorn"), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
     ap.add_argument("--sizes", default=None, help="with --design: comma-separated model widths (multiples of 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -535,7 +535,36 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a) {
 // ---- retention
 // float32 copies of head rows with the first `rot` values of each head rotated at the token's position: src [T, ld] holds
 // `heads` rows of D values per token from column 0 on; cs [T, rot / 2] (cos, sin); style 0 pairs (2i, 2i + 1), 1 pairs
-// (i, i + rot / 2).  Heads from `scale_from` on are multiplied by `scale` after the rotation.  One thread per value.
+// (i, i + rot / 2).  Heads from `scale_from` on are multiplied by `scale` after the rotation.  Heads of an even size: one CTA
+// row per token, one thread per pair of values (a rotated pair, or two neighbours behind the rotated part); else one thread
+// per value.
+template <typename T>
+__global__ void __launch_bounds__(256) rotate_head_pairs_kernel(const T* __restrict__ src, long long ld, int heads, int D, int rot, int style,
+                                                                const float2* __restrict__ cs, int scale_from, float scale, float* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int hd = D >> 1, half = rot >> 1;
+    const int u = blockIdx.y * blockDim.x + threadIdx.x;               // pair u of the token's heads * D / 2
+    if (u >= heads * hd) return;
+    const long long t = blockIdx.x;
+    const int h = u / hd, p = u - h * hd;
+    const T* x = src + t * ld + (size_t)h * D;
+    float* o = out + (t * heads + h) * D;
+    const float sc = h >= scale_from ? scale : 1.0f;
+    int ia, ib;
+    if (p < half) {
+        if (style == 1) { ia = p; ib = p + half; } else { ia = 2 * p; ib = ia + 1; }
+        const float2 c = cs[t * half + p];
+        const float a = to_f32(x[ia]), b = to_f32(x[ib]);
+        const float ra = (a * c.x - b * c.y) * sc, rb = (b * c.x + a * c.y) * sc;
+        if (style == 1) { o[ia] = ra; o[ib] = rb; }
+        else *reinterpret_cast<float2*>(o + ia) = make_float2(ra, rb);      // (D is even: the pair is 8-byte aligned)
+    } else {
+        ia = 2 * p;
+        *reinterpret_cast<float2*>(o + ia) = make_float2(to_f32(x[ia]) * sc, to_f32(x[ia + 1]) * sc);
+    }
+}
+
+
 template <typename T>
 __global__ void rotate_heads_kernel(const T* __restrict__ src, long long ld, int T_, int heads, int D, int rot, int style,
                                     const float2* __restrict__ cs, int scale_from, float scale, float* __restrict__ out) {
@@ -844,6 +873,15 @@ extern "C" int ttie_rotate_heads(const void* src, long long ld, int T, int heads
     const long long total = (long long)T * heads * D;
     const int grid = (int)((total + 255) / 256 < 148LL * 32 ? (total + 255) / 256 : 148LL * 32);
     cudaStream_t s = (cudaStream_t)stream;
+    const long long units = (long long)heads * (D / 2);
+    if (D % 2 == 0 && (units + 255) / 256 <= 65535) {
+        const dim3 pg((unsigned)T, (unsigned)((units + 255) / 256));
+        if (dtype == kF32) TTIE_LAUNCH(rotate_head_pairs_kernel<float>, pg, 256, 0, s, (const float*)src, ld, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
+        else if (dtype == kBF16) TTIE_LAUNCH(rotate_head_pairs_kernel<__nv_bfloat16>, pg, 256, 0, s, (const __nv_bfloat16*)src, ld, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
+        else TTIE_FAIL("rotate_heads: unknown dtype %d", dtype);
+        TTIE_CHECK_LAUNCH("rotate_heads");
+        return 0;
+    }
     if (dtype == kF32) TTIE_LAUNCH(rotate_heads_kernel<float>, grid, 256, 0, s, (const float*)src, ld, T, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
     else if (dtype == kBF16) TTIE_LAUNCH(rotate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)src, ld, T, heads, D, rot, style, (const float2*)cs, scale_from, scale, out);
     else TTIE_FAIL("rotate_heads: unknown dtype %d", dtype);
