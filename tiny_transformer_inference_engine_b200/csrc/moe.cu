@@ -64,7 +64,7 @@ constexpr int MAX_EXPERTS = 512;
 // largest score (a shuffle reduction per choice).  Shared memory per warp: E scores, then the groups' ratings and keep flags.
 constexpr int ROUTE_WARPS = 4;
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, int keep, int group_top, int top,
+moe_route_kernel(const float* __restrict__ logits, long long ld, int T_, int E, int groups, int keep, int group_top, int top,
                  float scale, int renorm, int softmax, const float* __restrict__ correction, int* __restrict__ idx,
                  float* __restrict__ wts) {
     extern __shared__ float sm[];
@@ -79,14 +79,14 @@ moe_route_kernel(const float* __restrict__ logits, int T_, int E, int groups, in
     const int per = E / groups;
     if (softmax) {
         float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logits[(size_t)t * E + e]);
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logits[(size_t)t * ld + e]);
         mx = warp_max(mx);
         float sum = 0.f;
-        for (int e = lane; e < E; e += 32) { const float p = expf(logits[(size_t)t * E + e] - mx); s[e] = p; sum += p; }
+        for (int e = lane; e < E; e += 32) { const float p = expf(logits[(size_t)t * ld + e] - mx); s[e] = p; sum += p; }
         sum = warp_sum(sum);
         for (int e = lane; e < E; e += 32) s[e] = s[e] / sum;
     } else {
-        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * E + e]));
+        for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * ld + e]));
     }
     for (int e = lane; e < E; e += 32) c[e] = correction ? s[e] + correction[e] : s[e];
     __syncwarp();
@@ -390,14 +390,14 @@ extern "C" int ttie_glu(const void* gate_up, long long ld, void* out, int T, int
 extern "C" int ttie_moe_max_experts() { return MAX_EXPERTS; }
 extern "C" int ttie_moe_tile_rows() { return BM; }
 
-extern "C" int ttie_moe_route(const float* logits, int T, int E, int groups, int keep, int group_top, int top, float scale, int renorm,
+extern "C" int ttie_moe_route(const float* logits, long long ld, int T, int E, int groups, int keep, int group_top, int top, float scale, int renorm,
                               int softmax, const float* correction, int* idx, float* wts, void* stream) {
     if (T <= 0) return 0;
     if (E < 1 || E > MAX_EXPERTS || groups < 1 || E % groups || keep < 1 || keep > groups || top < 1 || top > keep * (E / groups)
         || group_top < 1 || group_top > 2)
         TTIE_FAIL("moe_route: %d experts in %d groups, keep %d, group score of %d, top %d", E, groups, keep, group_top, top);
     TTIE_LAUNCH(moe_route_kernel, ceil_div(T, ROUTE_WARPS), ROUTE_WARPS * 32, (size_t)ROUTE_WARPS * (2 * E + 2 * groups) * sizeof(float),
-                (cudaStream_t)stream, logits, T, E, groups, keep, group_top, top, scale, renorm, softmax, correction, idx, wts);
+                (cudaStream_t)stream, logits, ld, T, E, groups, keep, group_top, top, scale, renorm, softmax, correction, idx, wts);
     TTIE_CHECK_LAUNCH("moe_route");
     return 0;
 }

@@ -69,7 +69,7 @@ _SIGNATURES = {
                         _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void, _c_int, _c_void,
                         _c_int, _c_void],
     "ttie_glu": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void],
-    "ttie_moe_route": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
+    "ttie_moe_route": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
     "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
@@ -1145,12 +1145,13 @@ class CudaOps:
         return out
 
     def moe_route(self, logits, groups, keep, group_top, top, scale, renorm=False, score="sigmoid", correction=None):
-        """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E].  ``score``: "sigmoid" per
+        """(expert ids int32 [T, top], weights float32 [T, top]) from float32 router logits [T, E] (rows may lie further apart
+        than E).  ``score``: "sigmoid" per
         expert or "softmax" over all of them; ``correction`` float32 [E]: added to the scores for the choice only."""
         T, E = logits.shape
         idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
         wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-        self._check(self.lib.ttie_moe_route(_ptr(logits), T, E, groups, keep, group_top, top, float(scale), 1 if renorm else 0,
+        self._check(self.lib.ttie_moe_route(_ptr(logits), logits.stride(0), T, E, groups, keep, group_top, top, float(scale), 1 if renorm else 0,
                                             {"sigmoid": 0, "softmax": 1}[score], _ptr(correction), _ptr(idx), _ptr(wts),
                                             self._stream(logits)), "moe_route")
         self.launches += 1

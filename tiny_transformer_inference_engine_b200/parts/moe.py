@@ -74,6 +74,9 @@ class GroupedMoE(FeedForward):
     def load(self, params):
         E = self.experts
         self.w_router = params[self.names["router"]].contiguous()
+        if self.routed % 8:                                              # rows of zeros up to a multiple of 8: the library's product
+            pad = self.w_router.new_zeros((-self.routed % 8, self.w_router.shape[1]))     # of many rows wants 32-byte rows of logits
+            self.w_router = torch.cat([self.w_router, pad], dim=0).contiguous()
         if self.has_correction:
             self.correction = params[self.names["correction"]].float().contiguous()
         if E == 0:                                                       # (identity experts only: nothing to multiply)
@@ -90,7 +93,7 @@ class GroupedMoE(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         ops, T = self.ops, x.shape[0]
-        logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)
+        logits = ops.linear(x, self.w_router, None, out_dtype=torch.float32)[:, :self.routed]
         idx, wts = ops.moe_route(logits, self.groups, self.keep, self.group_top, self.top, self.scale, self.renorm,
                                  score=self.score, correction=self.correction)
         plan = ops.moe_plan(idx, self.routed, identity=self.identity)
