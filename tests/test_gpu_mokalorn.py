@@ -394,6 +394,35 @@ def test_retention_alone(ops, dtype, heads, dim, vdim, decay, rot):
                 assert (err > 3e-2).sum() <= 3, (cuts[:4], i, err.max())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,dim,vdim,decay", [
+    (4, 16, 12, (1.0, 0.99, 0.6, 0.0)),
+    (2, 64, 40, (0.999, 0.9)),
+    (2, 128, 20, (0.97, 1.0)),
+    (1, 160, 24, (0.95,)),
+    (2, 48, 8, (0.5, 0.98)),                                            # padded to 64 channels
+])
+def test_retention_long_prompts_in_parts(ops, dtype, heads, dim, vdim, decay):
+    """Prompts long enough that a step walks them in parts (two launches): a long request beside a short one and beside one
+    of a single token, whole and cut so that later steps are short again; heads that forget nothing, little, fast and
+    everything; a state that the step finds filled (the second and third cut)."""
+    L = retention_layer(heads, dim, vdim, decay, {"base": 200.0, "dims": 8})
+    part, w = part_with_weights("mixer", _mixer(L, "a", 40, 1e-5), dtype, ops, 14, scale=0.3)
+    g = torch.Generator().manual_seed(15)
+    lens = (1500, 90, 1)
+    xs = [(torch.randn(n, 40, generator=g) * 0.5).to(DT[dtype]) for n in lens]
+    assert ops.retention_parts(sum(lens), 3) > 1 and ops.retention_parts(700 + 90 + 1, 3) > 1
+    exps = [pm.retention(x.double(), w, "", L["mixer"], 1e-5) for x in xs]
+    for cuts in ([1500], [700, 800], [3, 1400, 1, 96]):
+        outs = run_retention(part, ops, dtype, xs, cuts, slots=[1, 3, 0], state_rows=4)
+        for i in range(3):
+            err = (outs[i].double().cpu() - exps[i]).abs().max(dim=-1).values / exps[i].abs().max()
+            if dtype == "float32":
+                assert err.max() < 5e-5, (cuts, i, int(err.argmax()))
+            else:                                                      # (the head that keeps nothing: see test_retention_alone)
+                assert (err > 3e-2).sum() <= len(err) // 100 + 1, (cuts, i, err.max())
+
+
 def test_retention_keeps_a_far_token_by_its_decay(ops):
     """One early token brings a large key and value.  The head that does not decay still reads it 400 tokens later (whole, in
     portions and decoded), the head with a decay of 0.9 has lost it: the two heads' outputs are told apart before the head norm

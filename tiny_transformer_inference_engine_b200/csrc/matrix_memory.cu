@@ -599,7 +599,18 @@ struct RetArgs {
     const int* qsl; const int* slot_ids;
     float* out;                                                       // [T, H*Dv] float32
     int H, D, Dv, Dpad, slices, tb; bool vec;
+    float* scratch; int parts, mode;                                  // [requests * parts, H, Dv, Dpad]; see below
 };
+
+// Long prompts in parts.  The decay is one number per head, so the state behind token t of a request is
+//     decay^t S_0 + sum over the parts j that end at or before t of decay^(t - end_j) P_j,   P_j = sum_(u in part j) decay^(end_j - 1 - u) k_u v_u^T,
+// and a part's P_j needs no other part.  With ``parts`` > 1 the kernel runs twice over a grid of requests x parts: mode 1 walks
+// every part but a request's last from a zero state without reading out and leaves P_j in ``scratch`` (the unit of the last
+// part copies the request's state row there meanwhile, so that the second launch reads nothing that it also writes); mode 0
+// builds each part's first state from those, walks the part with read-out, and the request's last part writes the state row.
+// A request's part is max(128, its tokens / parts rounded up to 64) tokens, so a request of few tokens is one part and runs as
+// it does with parts == 1.
+constexpr int PART_MIN_TOKENS = 128;
 
 template <typename T, int KPT, int SL>
 __global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
@@ -610,21 +621,56 @@ __global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
     float* q_s = reinterpret_cast<float*>(smem_raw);                                  // [2][TB][Dpad]
     float* k_s = q_s + 2 * TB * a.Dpad;
     float* v_s = k_s + 2 * TB * a.Dpad;                                               // [TB][cols]
-    const int s = blockIdx.z, h = blockIdx.y;
-    const int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
+    const int s = blockIdx.z / a.parts, p = blockIdx.z - s * a.parts, h = blockIdx.y;
+    int t0 = a.qsl[s], n = a.qsl[s + 1] - t0;
+    int L = n, p_last = 0;                                           // tokens of a part, the part of the request's last token
+    if (a.parts > 1 && n > 0) {
+        L = max(PART_MIN_TOKENS, ((n + a.parts - 1) / a.parts + 63) / 64 * 64);
+        p_last = (n - 1) / L;                                        // (< parts)
+    }
+    const bool local = a.mode == 1;
+    const bool copies = local && p_last > 0 && p == a.parts - 1;     // (never a part that mode 1 walks: those lie before p_last)
+    if (local ? (p >= p_last && !copies) : p > p_last) return;
     const int slice = threadIdx.x % SL, cl = threadIdx.x / SL;
     const int col = blockIdx.x * cols + cl;
     const bool colv = col < a.Dv;
     const int ch0 = slice * KPT;
     const size_t row = slot_row_(a.slot_ids[s], a.state_rows);
     float* sp = a.S + ((row * a.H + h) * a.Dv + (colv ? col : 0)) * a.Dpad + ch0;
-    float S[KPT];
+    auto scratch_at = [&](int part) {
+        return a.scratch + ((((size_t)s * a.parts + part) * a.H + h) * a.Dv + (colv ? col : 0)) * a.Dpad + ch0;
+    };
+    if (copies) {
+        if (colv)
 #pragma unroll
-    for (int i = 0; i < KPT; i += 4) {
-        const float4 x4 = colv ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-        S[i] = x4.x; S[i + 1] = x4.y; S[i + 2] = x4.z; S[i + 3] = x4.w;
+            for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(scratch_at(p) + i) = *reinterpret_cast<const float4*>(sp + i);
+        return;
     }
     const float decay = a.decay[h];
+    float S[KPT];
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) S[i] = 0.f;
+    if (colv && !local) {
+        if (p_last == 0) {
+#pragma unroll
+            for (int i = 0; i < KPT; i += 4) {
+                const float4 x4 = *reinterpret_cast<const float4*>(sp + i);
+                S[i] = x4.x; S[i + 1] = x4.y; S[i + 2] = x4.z; S[i + 3] = x4.w;
+            }
+        } else {                                                     // the state row as it was, then the parts before this one
+            for (int j = -1; j < p; ++j) {
+                const float f = powf(decay, (float)(p * L - (j + 1) * L));      // (0^0 = 1: a head that keeps nothing keeps its first state at p = 0)
+                const float* src = scratch_at(j < 0 ? a.parts - 1 : j);
+#pragma unroll
+                for (int i = 0; i < KPT; i += 4) {
+                    const float4 x4 = *reinterpret_cast<const float4*>(src + i);
+                    S[i] = fmaf(f, x4.x, S[i]); S[i + 1] = fmaf(f, x4.y, S[i + 1]); S[i + 2] = fmaf(f, x4.z, S[i + 2]); S[i + 3] = fmaf(f, x4.w, S[i + 3]);
+                }
+            }
+        }
+    }
+    t0 += p * L;
+    n = min(L, n - p * L);
     const float* qp = a.q + (size_t)t0 * a.ld_qk + h * a.D;
     const float* kp = a.k + (size_t)t0 * a.ld_qk + h * a.D;
     const T* vp = reinterpret_cast<const T*>(a.v) + (size_t)t0 * a.ld_v + h * a.Dv;
@@ -638,8 +684,9 @@ __global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
                 const bool in = ch0 + i < a.D;
                 const float kv = (in ? kp[(size_t)tt * a.ld_qk + ch0 + i] : 0.f) * vj;
                 S[i] = fmaf(decay, S[i], kv);
-                acc = fmaf(S[i], in ? qp[(size_t)tt * a.ld_qk + ch0 + i] : 0.f, acc);
+                acc = fmaf(S[i], (in && !local) ? qp[(size_t)tt * a.ld_qk + ch0 + i] : 0.f, acc);
             }
+            if (local) continue;
             acc = slices_sum<SL>(acc);
             if (slice == 0 && colv) a.out[(size_t)(t0 + tt) * ld_o + h * a.Dv + col] = acc;
         }
@@ -648,7 +695,7 @@ __global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
         for (int e = threadIdx.x; e < 2 * TB * a.Dpad; e += blockDim.x)
             if (e % a.Dpad >= a.D) { q_s[e] = 0.f; k_s[e] = 0.f; }
     auto stage = [&](int buf, int c0, int nb) {
-        stage_rows<float>(q_s + buf * TB * a.Dpad, a.Dpad, qp + (size_t)c0 * a.ld_qk, a.ld_qk, nb, a.D, a.vec);
+        if (!local) stage_rows<float>(q_s + buf * TB * a.Dpad, a.Dpad, qp + (size_t)c0 * a.ld_qk, a.ld_qk, nb, a.D, a.vec);
         stage_rows<float>(k_s + buf * TB * a.Dpad, a.Dpad, kp + (size_t)c0 * a.ld_qk, a.ld_qk, nb, a.D, a.vec);
         cp_async_commit();
     };
@@ -685,31 +732,35 @@ __global__ void __launch_bounds__(128) retention_scan_kernel(const RetArgs a) {
             if (tt < nb) {                                           // (the same for every thread of the CTA)
                 const float vj = v_s[tt * cols + cl];
                 float q_[KPT], k_[KPT];
-                lds_keys<KPT>(qb + tt * a.Dpad, q_);
                 lds_keys<KPT>(kb + tt * a.Dpad, k_);
-                float acc = 0.f;
 #pragma unroll
-                for (int i = 0; i < KPT; ++i) {
-                    S[i] = fmaf(decay, S[i], k_[i] * vj);
-                    acc = fmaf(S[i], q_[i], acc);
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(decay, S[i], k_[i] * vj);
+                if (!local) {                                        // (the same for every thread of the grid)
+                    lds_keys<KPT>(qb + tt * a.Dpad, q_);
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < KPT; ++i) acc = fmaf(S[i], q_[i], acc);
+                    part[tt] = acc;
                 }
-                part[tt] = acc;
             }
         }
-        int first = 0;
-        RunReduce<SL / 2, TB>::run(part, slice, first);
-        if (colv && RunOwner<SL, TB>::writes(slice)) {
+        if (!local) {
+            int first = 0;
+            RunReduce<SL / 2, TB>::run(part, slice, first);
+            if (colv && RunOwner<SL, TB>::writes(slice)) {
 #pragma unroll
-            for (int j = 0; j < RunOwner<SL, TB>::COUNT; ++j)
-                if (first + j < nb) a.out[(size_t)(t0 + c0 + first + j) * ld_o + h * a.Dv + col] = part[j];
+                for (int j = 0; j < RunOwner<SL, TB>::COUNT; ++j)
+                    if (first + j < nb) a.out[(size_t)(t0 + c0 + first + j) * ld_o + h * a.Dv + col] = part[j];
+            }
         }
         __syncthreads();
     }
     }
     pdl_launch_dependents();
-    if (colv) {
+    if (colv && (local || p == p_last)) {
+        float* dst = local ? scratch_at(p) : sp;
 #pragma unroll
-        for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+        for (int i = 0; i < KPT; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
     }
 }
 
@@ -891,21 +942,29 @@ extern "C" int ttie_rotate_heads(const void* src, long long ld, int T, int heads
 
 extern "C" int ttie_retention_scan(const float* q, const float* k, long long ld_qk, const void* v, long long ld_v, const float* decay,
                                    float* S, int state_rows, const int* qsl, const int* slot_ids, int num_seqs, float* out, int H, int D,
-                                   int Dv, int dtype, void* stream) {
+                                   int Dv, int parts, float* scratch, int dtype, void* stream) {
     if (num_seqs <= 0) return 0;
+    if (parts < 1 || (parts > 1 && scratch == nullptr) || (long long)num_seqs * parts > 65535)
+        TTIE_FAIL("retention_scan: %d parts for %d requests (scratch %p)", parts, num_seqs, (void*)scratch);
     RetArgs a;
     a.q = q; a.k = k; a.ld_qk = ld_qk; a.v = v; a.ld_v = ld_v; a.decay = decay; a.S = S; a.state_rows = state_rows;
-    a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv;
+    a.qsl = qsl; a.slot_ids = slot_ids; a.out = out; a.H = H; a.D = D; a.Dv = Dv; a.scratch = scratch; a.parts = parts; a.mode = 0;
     int threads, kpt;
-    if (scan_shape(D, Dv, num_seqs * H, &kpt, &a.slices, &threads)) TTIE_FAIL("retention_scan: %d key channels per head (at most 512)", D);
+    if (scan_shape(D, Dv, num_seqs * parts * H, &kpt, &a.slices, &threads)) TTIE_FAIL("retention_scan: %d key channels per head (at most 512)", D);
     a.Dpad = a.slices * kpt;
     const int cols = threads / a.slices;
     a.tb = 64 / kpt;
     if (threads * MAXV < a.tb * cols) TTIE_FAIL("retention_scan: internal: %d threads cannot carry %d x %d values", threads, a.tb, cols);
     const size_t smem = (size_t)2 * a.tb * a.Dpad * 2 * 4 + (size_t)a.tb * cols * 4;
     a.vec = D % 4 == 0 && ld_qk % 4 == 0 && !(((uintptr_t)q | (uintptr_t)k) & 15);
-    dim3 grid(ceil_div(Dv, cols), H, num_seqs);
+    dim3 grid(ceil_div(Dv, cols), H, num_seqs * parts);
     cudaStream_t s = (cudaStream_t)stream;
+    if (parts > 1) {                                                 // every part's own sum, from a zero state
+        a.mode = 1;
+        TTIE_SCAN_DISPATCH(retention_scan_kernel, RetArgs);
+        TTIE_CHECK_LAUNCH("retention_scan (parts)");
+        a.mode = 0;
+    }
     TTIE_SCAN_DISPATCH(retention_scan_kernel, RetArgs);
     TTIE_CHECK_LAUNCH("retention_scan");
     return 0;

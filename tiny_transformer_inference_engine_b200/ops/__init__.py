@@ -92,7 +92,7 @@ _SIGNATURES = {
                         _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ttie_rotate_heads": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_float, _c_void, _c_int, _c_void],
     "ttie_retention_scan": [_c_void, _c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int,
-                            _c_int, _c_int, _c_int, _c_void],
+                            _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_head_norm_gate": [_c_void, _c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void, _c_int, _c_void],
     "ttie_activation": [_c_void, _c_void, _c_ll, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ttie_matrix_state_pad": [_c_int],
@@ -1086,16 +1086,32 @@ class CudaOps:
     def retention_scan(self, q, k, v, decay, S, query_start_loc, slot_ids, num_seqs, num_heads, dim, v_dim):
         """Retention's recurrence over the step's tokens from the state rows S [slots + 1, H, v_dim, padded dim] (advanced in
         place): S <- decay_h S + k v^T, o = S^T q.  q, k float32 [T, H*dim] views with one row stride; v [T, H*v_dim] in the
-        compute dtype, a view with a row stride; ``decay`` float32 [H].  Returns o float32 [T, H*v_dim]."""
+        compute dtype, a view with a row stride; ``decay`` float32 [H].  Returns o float32 [T, H*v_dim].
+
+        A step that may hold a long prompt (the step's tokens less one for every other request: the host knows no more, and
+        the number holds for a captured graph) is walked in ``parts`` (``retention_parts``) by two launches: the decay is a
+        constant, so every part's own sum needs no other part and the parts' first states follow from those sums."""
         T = q.shape[0]
         out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
         if q.stride(0) != k.stride(0) or q.dtype != torch.float32 or k.dtype != torch.float32:
             raise KernelError("retention_scan: q and k must be float32 and share a row stride")
+        parts = self.retention_parts(T, int(num_seqs))
+        scratch = torch.empty((int(num_seqs) * parts,) + tuple(S.shape[1:]), dtype=torch.float32, device=q.device) if parts > 1 else None
         self._check(self.lib.ttie_retention_scan(_ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(decay), _ptr(S), S.shape[0],
                                                  _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads, dim, v_dim,
-                                                 self._dt(v), self._stream(q)), "retention_scan")
-        self.launches += 1
+                                                 parts, _ptr(scratch), self._dt(v), self._stream(q)), "retention_scan")
+        self.launches += 2 if parts > 1 else 1
         return out
+
+    retention_part_tokens = 256             # a long prompt is walked in parts of about this many tokens,
+    retention_max_parts = 16                # at most this many a request,
+    retention_max_units = 64                # and requests x parts (state-sized scratch rows) at most this
+
+    def retention_parts(self, num_tokens: int, num_seqs: int) -> int:
+        longest = num_tokens - (num_seqs - 1)                          # the most tokens one request of the step can bring
+        if longest < 2 * self.retention_part_tokens:
+            return 1
+        return max(1, min(self.retention_max_parts, longest // self.retention_part_tokens, self.retention_max_units // num_seqs))
 
     def head_norm_gate(self, o, gate, weight, num_heads, v_dim, eps, act):
         """out = o / rms(o over each head) * weight * act(gate); o float32 [T, H*v_dim], gate a view [T, H*v_dim] with a row
