@@ -411,7 +411,9 @@ def test_retention_long_prompts_in_parts(ops, dtype, heads, dim, vdim, decay):
     g = torch.Generator().manual_seed(15)
     lens = (1500, 90, 1)
     xs = [(torch.randn(n, 40, generator=g) * 0.5).to(DT[dtype]) for n in lens]
-    assert ops.retention_parts(sum(lens), 3) > 1 and ops.retention_parts(700 + 90 + 1, 3) > 1
+    state = part.cache_needs()[0].shape
+    assert ops.retention_parts(sum(lens), 3, state[0] * state[1] * state[2]) > 1 and ops.retention_parts(700 + 90 + 1, 3) > 1
+    assert ops.retention_parts(sum(lens), 3, 1 << 20) == 1 and ops.retention_parts(300, 3) == 1
     exps = [pm.retention(x.double(), w, "", L["mixer"], 1e-5) for x in xs]
     for cuts in ([1500], [700, 800], [3, 1400, 1, 96]):
         outs = run_retention(part, ops, dtype, xs, cuts, slots=[1, 3, 0], state_rows=4)

@@ -1095,7 +1095,7 @@ class CudaOps:
         out = torch.empty((T, num_heads * v_dim), dtype=torch.float32, device=q.device)
         if q.stride(0) != k.stride(0) or q.dtype != torch.float32 or k.dtype != torch.float32:
             raise KernelError("retention_scan: q and k must be float32 and share a row stride")
-        parts = self.retention_parts(T, int(num_seqs))
+        parts = self.retention_parts(T, int(num_seqs), S[0].numel())
         scratch = torch.empty((int(num_seqs) * parts,) + tuple(S.shape[1:]), dtype=torch.float32, device=q.device) if parts > 1 else None
         self._check(self.lib.ttie_retention_scan(_ptr(q), _ptr(k), q.stride(0), _ptr(v), v.stride(0), _ptr(decay), _ptr(S), S.shape[0],
                                                  _ptr(query_start_loc), _ptr(slot_ids), int(num_seqs), _ptr(out), num_heads, dim, v_dim,
@@ -1105,11 +1105,16 @@ class CudaOps:
 
     retention_part_tokens = 256             # a long prompt is walked in parts of about this many tokens,
     retention_max_parts = 16                # at most this many a request,
-    retention_max_units = 64                # and requests x parts (state-sized scratch rows) at most this
+    retention_max_units = 64                # and requests x parts (state-sized scratch rows) at most this;
+    retention_parts_state = 160 * 1024      # only where a request's state has at most this many elements
 
-    def retention_parts(self, num_tokens: int, num_seqs: int) -> int:
+    def retention_parts(self, num_tokens: int, num_seqs: int, state_elems: int = 0) -> int:
+        """Parts cost half as much work again (every part but the last is walked twice, once without read-out) and buy
+        warps.  Measured on one 2,048-token prompt: a state of 8 heads x 128 x 128 takes 450 us in one piece (bound by the
+        chain of tokens: twice the heads take the same time) and 320-350 us in 8 parts (bound by issued instructions: twice
+        the heads take twice the time), so parts pay up to about 160 K state elements a request."""
         longest = num_tokens - (num_seqs - 1)                          # the most tokens one request of the step can bring
-        if longest < 2 * self.retention_part_tokens:
+        if longest < 2 * self.retention_part_tokens or state_elems > self.retention_parts_state:
             return 1
         return max(1, min(self.retention_max_parts, longest // self.retention_part_tokens, self.retention_max_units // num_seqs))
 
