@@ -33,6 +33,8 @@ struct MmaParams {
     float cap_in, cap_out;              // score softcap: raw score s becomes cap_out * tanh(s * cap_in) (cap_in 0: none)
     int row_tiles, num_splits, split_len;
     float* ws_o; float* ws_ml;
+    int sigmoid;                        // 1 (tile loop only): a visible key weighs sigmoid(score + head_bias[head]), nothing is normalised
+    const float* head_bias;             // [Hq] or null
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -126,6 +128,12 @@ paged_attn_mma_kernel(const MmaParams p) {
     const int wpos_hi = warp_active ? ctx + wrow_hi / G : -1;
     const int wpos_lo = warp_active ? ctx + wrow_lo / G : -1;
     const int wkey_lo = first_visible_key(wpos_lo, p.window, p.chunk);
+    // sigmoid weights: the bias of each row's head, in units of log2 e like the scaled scores
+    float hb2[2] = {0.f, 0.f};
+    if (p.sigmoid && p.head_bias) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) if (rvalid[h]) hb2[h] = p.head_bias[kvh * G + rrow[h] % G] * 1.4426950408889634f;
+    }
 
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[D / 8][4];
@@ -237,6 +245,18 @@ paged_attn_mma_kernel(const MmaParams p) {
                     mx[h] = fmaxf(mx[h], v);
                 }
             }
+            if (p.sigmoid) {
+                // 1 / (1 + 2^-(score + bias)) per key; a masked key (-inf) gives 1 / (1 + inf) = 0; nothing to rescale
+#pragma unroll
+                for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float r;
+                        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + ex2(-fmaf(s[i][e], p.scale_log2, hb2[e >> 1]))));
+                        s[i][e] = r;
+                    }
+                }
+            } else {
             float alpha[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -259,6 +279,7 @@ paged_attn_mma_kernel(const MmaParams p) {
             }
 #pragma unroll
             for (int i = 0; i < D / 8; ++i) { o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1]; }
+            }
             // O += P V
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk) {
@@ -290,7 +311,7 @@ paged_attn_mma_kernel(const MmaParams p) {
         const int tok = row / G, g = row - tok * G;
         const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
         if (p.num_splits == 1) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float inv = p.sigmoid ? 1.f : l > 0.f ? 1.f / l : 0.f;
             __nv_bfloat16* op = p.out + grow * D + 2 * (lane & 3);
 #pragma unroll
             for (int i = 0; i < D / 8; ++i)
@@ -301,8 +322,8 @@ paged_attn_mma_kernel(const MmaParams p) {
             for (int i = 0; i < D / 8; ++i) *reinterpret_cast<float2*>(wo + i * 8) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
             if ((lane & 3) == 0) {
                 float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
-                ml[0] = m_run[h] * 0.6931471805599453f;             // back to natural-log units for the merge
-                ml[1] = l;
+                ml[0] = p.sigmoid ? 0.f : m_run[h] * 0.6931471805599453f;   // back to natural-log units for the merge
+                ml[1] = p.sigmoid ? 1.0f / (float)p.num_splits : l;         // (sigmoid weights: the pieces simply add)
             }
         }
     }
@@ -789,12 +810,31 @@ extern "C" int ttie_paged_attention_mma(const void* q, long long q_stride, const
                                          T, num_seqs, Hq, Hkv, D, max_q_len, scale, softcap, window, chunk, num_splits, split_len, scratch, 0, stream);
 }
 
+// weights 0: softmax; 1 (form 0 only): sigmoid(score + head_bias[head]) per visible key (head_bias float32 [Hq] or null)
+extern "C" int ttie_paged_attention_mma_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                                const int* block_table, int table_width, int page_size, const int* qsl,
+                                                const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                                int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                                float* scratch, int form, int weights, const float* head_bias, void* stream);
+
 extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                              const int* block_table, int table_width, int page_size, const int* qsl,
                                              const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
                                              int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                              float* scratch, int form, void* stream) {
+    return ttie_paged_attention_mma_weights(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out, T, num_seqs,
+                                            Hq, Hkv, D, max_q_len, scale, softcap, window, chunk, num_splits, split_len, scratch, form, 0, nullptr,
+                                            stream);
+}
+
+extern "C" int ttie_paged_attention_mma_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                                const int* block_table, int table_width, int page_size, const int* qsl,
+                                                const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                                int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                                float* scratch, int form, int weights, const float* head_bias, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
+    if (weights != 0 && weights != 1) TTIE_FAIL("paged_attention_mma: unknown kind of weights %d", weights);
+    if (weights == 1 && form != 0) TTIE_FAIL("paged_attention_mma: sigmoid weights run in the tile loop only");
     if (!ttie_attn_mma_supported(D)) TTIE_FAIL("paged_attention_mma: head size %d not supported (multiples of 16 up to 128)", D);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("paged_attention_mma: %d heads are not a multiple of %d kv heads", Hq, Hkv);
     if (q_stride % 8) TTIE_FAIL("paged_attention_mma: query row stride %lld must be a multiple of 8 elements", q_stride);
@@ -812,6 +852,7 @@ extern "C" int ttie_paged_attention_mma_form(const void* q, long long q_stride, 
     p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.chunk = chunk;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.num_splits = num_splits; p.split_len = split_len;
+    p.sigmoid = weights; p.head_bias = head_bias;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     const int rows = max_q_len * (Hq / Hkv);
     if (form == 2 || form == 4) {

@@ -14,6 +14,10 @@
 // attention all heads of a token share each key/value tile loaded into shared memory.  With
 // more than one split the CTAs leave unnormalised partial outputs and (max, sum) pairs in
 // scratch memory and a second kernel merges them.
+//
+// Sigmoid weights (instead of a softmax): the weight of a visible key is sigmoid(score + bias of the row's head), weights are
+// not normalised over keys, so a row's output is a plain sum and the pieces of a cut key range simply add: each piece leaves
+// (maximum 0, sum 1 / pieces) beside its partial output, with which the merge kernels' formula is that plain sum.
 #include "common.cuh"
 #include <math.h>
 using namespace ttie;
@@ -30,6 +34,8 @@ struct AttnParams {
     int num_seqs, Hq, Hkv, D;
     float scale; int window, chunk;
     float softcap;                 // > 0: scores pass cap * tanh(score / cap) before mask and softmax
+    int sigmoid;                   // 1: a visible key weighs sigmoid(score + head_bias[head]); no softmax
+    const float* head_bias;        // [Hq] or null (sigmoid weights only)
     int row_tiles;                 // tiles of ROWS query rows per (request, kv head)
     int num_splits, split_len;
     float* ws_o; float* ws_ml;     // [T*Hq, num_splits, D] and [T*Hq, num_splits, 2]
@@ -78,6 +84,7 @@ paged_attn_simt_kernel(const AttnParams p) {
     float m[RPW], l[RPW], o[RPW][DPL];
     int pos[RPW], lo[RPW];
     bool valid[RPW];
+    float hb[RPW];
 #pragma unroll
     for (int r = 0; r < RPW; ++r) {
         const int row = row0 + warp * RPW + r;
@@ -85,6 +92,7 @@ paged_attn_simt_kernel(const AttnParams p) {
         const int tok = valid[r] ? row / G : 0;
         pos[r] = ctx + tok;
         lo[r] = first_visible_key(pos[r], p.window, p.chunk);
+        hb[r] = (p.sigmoid && p.head_bias && valid[r]) ? p.head_bias[kvh * G + (row - tok * G)] : 0.f;
         m[r] = -INFINITY; l[r] = 0.f;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) o[r][i] = 0.f;
@@ -147,6 +155,7 @@ paged_attn_simt_kernel(const AttnParams p) {
                 const bool vis = valid[r] && key < k_hi && key <= pos[r] && key >= lo[r];
                 float sv = s[r] * p.scale;
                 if (p.softcap > 0.f) sv = p.softcap * tanhf(sv / p.softcap);
+                if (p.sigmoid) { pr[r] = vis ? 1.0f / (1.0f + expf(-(sv + hb[r]))) : 0.f; continue; }
                 const float sc = vis ? sv : -INFINITY;
                 const float m_new = fmaxf(m[r], warp_max(sc));
                 const float alpha = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
@@ -183,7 +192,7 @@ paged_attn_simt_kernel(const AttnParams p) {
         const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
         if (p.num_splits == 1) {
             T* op = (T*)p.out + grow * D;
-            const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+            const float inv = p.sigmoid ? 1.f : l[r] > 0.f ? 1.f / l[r] : 0.f;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 const int d = lane + 32 * i;
@@ -198,7 +207,7 @@ paged_attn_simt_kernel(const AttnParams p) {
             }
             if (lane == 0) {
                 float* ml = p.ws_ml + (grow * p.num_splits + split) * 2;
-                ml[0] = m[r]; ml[1] = l[r];
+                ml[0] = p.sigmoid ? 0.f : m[r]; ml[1] = p.sigmoid ? 1.0f / (float)p.num_splits : l[r];
             }
         }
     }
@@ -406,11 +415,28 @@ extern "C" long long ttie_attn_scratch_floats(int T, int Hq, int D, int num_spli
     return num_splits > 1 ? (long long)T * Hq * num_splits * (D + 2) : 0;
 }
 
+// weights 0: softmax over the visible keys; 1: sigmoid(score + head_bias[head]) per visible key (head_bias float32 [Hq] or null)
+extern "C" int ttie_paged_attention_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                            const int* block_table, int table_width, int page_size, const int* qsl,
+                                            const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                            int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                            float* scratch, int dtype, int weights, const float* head_bias, void* stream);
+
 extern "C" int ttie_paged_attention(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                     const int* block_table, int table_width, int page_size, const int* qsl,
                                     const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
                                     int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
                                     float* scratch, int dtype, void* stream) {
+    return ttie_paged_attention_weights(q, q_stride, k_pages, v_pages, block_table, table_width, page_size, qsl, seq_lens, out, T, num_seqs,
+                                        Hq, Hkv, D, max_q_len, scale, softcap, window, chunk, num_splits, split_len, scratch, dtype, 0, nullptr,
+                                        stream);
+}
+
+extern "C" int ttie_paged_attention_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                            const int* block_table, int table_width, int page_size, const int* qsl,
+                                            const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                            int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                            float* scratch, int dtype, int weights, const float* head_bias, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
     if (D % 4 || D > 512 || D <= 0) TTIE_FAIL("paged_attention: head size %d not supported (multiples of 4 up to 512)", D);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("paged_attention: %d heads are not a multiple of %d kv heads", Hq, Hkv);
@@ -422,6 +448,8 @@ extern "C" int ttie_paged_attention(const void* q, long long q_stride, const voi
     p.block_table = block_table; p.table_width = table_width; p.page_size = page_size;
     p.qsl = qsl; p.seq_lens = seq_lens; p.out = out;
     p.num_seqs = num_seqs; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.scale = scale; p.window = window; p.chunk = chunk; p.softcap = softcap;
+    if (weights != 0 && weights != 1) TTIE_FAIL("paged_attention: unknown kind of weights %d", weights);
+    p.sigmoid = weights; p.head_bias = head_bias;
     const int G = Hq / Hkv;
     p.row_tiles = ceil_div(max_q_len * G, ROWS);
     p.num_splits = num_splits; p.split_len = split_len;

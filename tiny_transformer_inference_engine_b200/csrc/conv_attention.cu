@@ -15,6 +15,10 @@
 //                         value head is the key head as it stands before norm and rotation.
 //   conv_tail_update      moves the step's last taps - 1 projected rows into the state rows (a request that brought fewer
 //                         keeps the newest of its old ones); runs after the kernel above has read the old rows.
+//   stream_conv           the same convolution over the rows of the 32-bit residual stream (every channel of the model's width),
+//                         for layers whose mixer reads x + conv(x): weights tap-major in 32-bit (the caller adds 1 to the last
+//                         tap for the x itself), state rows as above with the last taps - 1 stream rows, output in the compute
+//                         dtype; conv_tail_update (32-bit rows) advances the state
 //   gate_head_rows        out[t, h, :Dv] = attn[t, h, :Dv] * sigmoid(gate) (gate optional: one number per head, gate[t, h], or
 //                         one per value, gate[t, h * Dv + j]), dropping the padding.
 #include "common.cuh"
@@ -31,6 +35,8 @@ struct QkvArgs {
     const int* positions; const int* token_seq; const int* qsl; const int* slot_ids;
     const float2* cs; int rot; int style;
     const float* norm_w; float norm_eps;                            // [2][D]: the query heads' weights, then the key heads'; null: no norm
+    const float* row_inv;                                           // [T][2]: 1 / rms of the token's whole q and whole k projection (one norm over
+                                                                    // all heads at once; norm_w is then [Hq*D + Hkv*D], a weight per channel); null: a norm per head
     int v_from_k;                                                   // the values are the key heads before norm and rotation
     float qt_coef; int qt_every;                                    // query temperature; every 0: none
     void* q_out; void* k_pages; void* v_pages;
@@ -44,6 +50,11 @@ __device__ __forceinline__ int value_col0(const QkvArgs& a, int h) { return a.v_
 // what a query at position pos is multiplied by
 __device__ __forceinline__ float query_temperature(const QkvArgs& a, int pos) {
     return a.qt_every > 0 ? 1.0f + a.qt_coef * logf((float)((pos + 1) / a.qt_every) + 1.0f) : 1.0f;
+}
+
+// first norm weight of head h of kind 0 (q) or 1 (k)
+__device__ __forceinline__ int norm_w0(const QkvArgs& a, int kind, int h) {
+    return a.row_inv ? (kind == 0 ? h * a.D : (a.Hq + h) * a.D) : kind * a.D;
 }
 
 // value i of a head row x after the rotation of its first `rot` values
@@ -95,11 +106,16 @@ __global__ void __launch_bounds__(128) qkv_conv_rope_store_kernel(const QkvArgs 
     }
     __syncthreads();
     if (a.norm_w && kind != 2) {                                    // the head over its root mean square, times the shared weight
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < a.D; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
-        ss = block_sum(ss, red);
-        const float inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
-        for (int i = threadIdx.x; i < a.D; i += blockDim.x) row[i] = row[i] * inv * a.norm_w[kind * a.D + i];
+        float inv;
+        if (a.row_inv) inv = a.row_inv[2 * (size_t)t + kind];
+        else {
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < a.D; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+            ss = block_sum(ss, red);
+            inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
+        }
+        const float* nw = a.norm_w + norm_w0(a, kind, h);
+        for (int i = threadIdx.x; i < a.D; i += blockDim.x) row[i] = row[i] * inv * nw[i];
         __syncthreads();
     }
     const float2* cs = a.rot > 0 ? a.cs + (size_t)t * (a.rot >> 1) : nullptr;
@@ -189,15 +205,18 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const Qkv
     float inv = 1.f;
     const bool normed = a.norm_w != nullptr && kind != 2;
     if (normed) {                                                    // (the same for all lanes of a head: they sit side by side)
-        float ss = 0.f;
+        if (a.row_inv) inv = a.row_inv[2 * (size_t)t + kind];
+        else {
+            float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(out[i], out[i], ss);
-        const unsigned lane = threadIdx.x & 31u;
-        const unsigned group = chunks >= 32 ? 0xffffffffu : ((1u << chunks) - 1u) << (lane & ~(unsigned)(chunks - 1));
-        for (int o = 1; o < chunks; o <<= 1) ss += __shfl_xor_sync(group, ss, o);
-        inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
+            for (int i = 0; i < 8; ++i) ss = fmaf(out[i], out[i], ss);
+            const unsigned lane = threadIdx.x & 31u;
+            const unsigned group = chunks >= 32 ? 0xffffffffu : ((1u << chunks) - 1u) << (lane & ~(unsigned)(chunks - 1));
+            for (int o = 1; o < chunks; o <<= 1) ss += __shfl_xor_sync(group, ss, o);
+            inv = 1.0f / sqrtf(ss / (float)a.D + a.norm_eps);
+        }
         if (inside) {
-            const float* w = a.norm_w + kind * a.D + i0;
+            const float* w = a.norm_w + norm_w0(a, kind, h) + i0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) out[i] = out[i] * inv * w[i];
         }
@@ -211,7 +230,7 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const Qkv
             float other[8];
             conv8(a, proj, tail, C, t, j, c0 + ip, other);
             if (normed) {
-                const float* w = a.norm_w + kind * a.D + ip;
+                const float* w = a.norm_w + norm_w0(a, kind, h) + ip;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) other[i] = other[i] * inv * w[i];
             }
@@ -248,6 +267,57 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_store_vec8_kernel(const Qkv
     if (page < 0 || page >= a.num_pages) page = 0;                  // validated on the host; never write outside
     const size_t dst = (((size_t)page * a.Hkv + h) * a.page_size + pos % a.page_size) * a.Dp + i0;
     *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(kind == 1 ? a.k_pages : a.v_pages) + dst) = packed;
+}
+
+// one warp per token: 1 / sqrt(mean(x^2) + eps) over the token's nq query channels and over its nk key channels (one norm over
+// the whole projection, before it is cut into heads); 32-bit
+template <typename T>
+__global__ void __launch_bounds__(128) proj_row_rms_kernel(const T* __restrict__ proj, long long ld, int T_, int nq, int nk, float eps,
+                                                           float* __restrict__ inv) {
+    TTIE_PDL_ENTRY();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T_) return;
+    const T* row = proj + (size_t)t * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < nq; i += 32) { const float v = to_f32(row[i]); sq = fmaf(v, v, sq); }
+    for (int i = lane; i < nk; i += 32) { const float v = to_f32(row[nq + i]); sk = fmaf(v, v, sk); }
+    sq = warp_sum(sq); sk = warp_sum(sk);
+    if (lane == 0) {
+        inv[2 * (size_t)t] = 1.0f / sqrtf(sq / (float)nq + eps);
+        inv[2 * (size_t)t + 1] = 1.0f / sqrtf(sk / (float)nk + eps);
+    }
+}
+
+// one thread per (token, four channels); x [T, C] 32-bit, w [taps][C], tail [slots + 1][taps - 1][C]
+template <typename TO, int V>
+__global__ void __launch_bounds__(128) stream_conv_kernel(const float* __restrict__ x, int T_, int C, int taps, const float* __restrict__ w,
+                                                          const float* __restrict__ tail, int tail_rows, const int* __restrict__ token_seq,
+                                                          const int* __restrict__ qsl, const int* __restrict__ slot_ids, TO* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (c >= C) return;
+    for (int t = blockIdx.y; t < T_; t += gridDim.y) {
+        const int s = token_seq[t];
+        const int j = t - qsl[s];                                   // index among the request's tokens of this step
+        const float* mine = taps > 1 ? tail + (size_t)slot_row_(slot_ids[s], tail_rows) * (taps - 1) * C : nullptr;
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int k = 0; k < taps; ++k) {
+            const int src = j - (taps - 1) + k;
+            const float* u = src >= 0 ? x + (size_t)(t - j + src) * C + c : mine + (size_t)(taps - 1 + src) * C + c;
+            const float* wk = w + (size_t)k * C + c;
+            if (V == 4) {
+                const float4 uv = *reinterpret_cast<const float4*>(u), wv = __ldg(reinterpret_cast<const float4*>(wk));
+                acc[0] = fmaf(wv.x, uv.x, acc[0]); acc[1 % V] = fmaf(wv.y, uv.y, acc[1 % V]);
+                acc[2 % V] = fmaf(wv.z, uv.z, acc[2 % V]); acc[3 % V] = fmaf(wv.w, uv.w, acc[3 % V]);
+            } else {
+                acc[0] = fmaf(wk[0], u[0], acc[0]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[(size_t)t * C + c + i] = from_f32<TO>(acc[i]);
+    }
 }
 
 template <typename T>
@@ -313,7 +383,7 @@ __global__ void gate_head_rows_vec8_kernel(const __nv_bfloat16* __restrict__ att
 extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, int Hq, int Hkv, int D, int Dv, int Dp, int taps,
                                         const float* conv_w, const float* tail, int tail_rows, const int* positions,
                                         const int* token_seq, const int* qsl, const int* slot_ids, const void* cs, int rot, int style,
-                                        const float* norm_w, float norm_eps, int v_from_k, float qt_coef, int qt_every,
+                                        const float* norm_w, float norm_eps, const float* row_inv, int v_from_k, float qt_coef, int qt_every,
                                         void* q_out, void* k_pages, void* v_pages, const int* block_table, int table_width,
                                         int page_size, int num_pages, int write_kv, int dtype, void* stream) {
     if (T <= 0) return 0;
@@ -323,10 +393,11 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     if (rot < 0 || rot > D || rot % 2) TTIE_FAIL("qkv_conv_rope_store: %d rotated values of a head of %d", rot, D);
     if (rot > 0 && !cs) TTIE_FAIL("qkv_conv_rope_store: a rotation needs the step's cos/sin table");
     if (taps < 1 || (taps > 1 && (!conv_w || !tail))) TTIE_FAIL("qkv_conv_rope_store: %d taps need weights and state rows", taps);
+    if (row_inv && (!norm_w || conv_w)) TTIE_FAIL("qkv_conv_rope_store: a norm over the whole projection needs weights and excludes a convolution");
     QkvArgs a;
     a.proj = proj; a.ld = ld; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.Dv = Dv; a.Dp = Dp; a.taps = taps; a.conv_w = conv_w; a.tail = tail;
     a.tail_rows = tail_rows; a.positions = positions; a.token_seq = token_seq; a.qsl = qsl; a.slot_ids = slot_ids;
-    a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.norm_w = norm_w; a.norm_eps = norm_eps; a.v_from_k = v_from_k;
+    a.cs = (const float2*)cs; a.rot = rot; a.style = style; a.norm_w = norm_w; a.norm_eps = norm_eps; a.row_inv = row_inv; a.v_from_k = v_from_k;
     a.qt_coef = qt_coef; a.qt_every = qt_every; a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages;
     a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages; a.write_kv = write_kv;
     const size_t smem = (size_t)(D > Dv ? D : Dv) * sizeof(float);
@@ -334,7 +405,7 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     cudaStream_t s = (cudaStream_t)stream;
     const bool aligned = !(((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)conv_w | (uintptr_t)tail) & 15);
     const int lanes = Dp / 8;                                        // of a head in the eight-values form; a norm adds up over them by shuffles
-    const bool norm_ok = !norm_w || (Dp % 8 == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0);
+    const bool norm_ok = !norm_w || row_inv || (Dp % 8 == 0 && lanes <= 32 && (lanes & (lanes - 1)) == 0);
     if (dtype == kBF16 && D % 8 == 0 && Dv % 8 == 0 && Dp % 8 == 0 && ld % 8 == 0 && aligned && norm_ok
         && (rot == 0 || rot % (style == 1 ? 16 : 8) == 0)) {
         const long long threads = (long long)T * (Hq + 2 * Hkv) * (Dp / 8);
@@ -348,6 +419,33 @@ extern "C" int ttie_qkv_conv_rope_store(const void* proj, long long ld, int T, i
     else if (dtype == kBF16) TTIE_LAUNCH(qkv_conv_rope_store_kernel<__nv_bfloat16>, grid, 128, smem, s, a);
     else TTIE_FAIL("qkv_conv_rope_store: unknown dtype %d", dtype);
     TTIE_CHECK_LAUNCH("qkv_conv_rope_store");
+    return 0;
+}
+
+extern "C" int ttie_proj_row_rms(const void* proj, long long ld, int T, int nq, int nk, float eps, float* inv, int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (nq <= 0 || nk <= 0) TTIE_FAIL("proj_row_rms: %d query and %d key channels", nq, nk);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kF32) TTIE_LAUNCH(proj_row_rms_kernel<float>, ceil_div(T, 4), 128, 0, s, (const float*)proj, ld, T, nq, nk, eps, inv);
+    else if (dtype == kBF16) TTIE_LAUNCH(proj_row_rms_kernel<__nv_bfloat16>, ceil_div(T, 4), 128, 0, s, (const __nv_bfloat16*)proj, ld, T, nq, nk, eps, inv);
+    else TTIE_FAIL("proj_row_rms: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("proj_row_rms");
+    return 0;
+}
+
+extern "C" int ttie_stream_conv(const float* x, int T, int C, int taps, const float* w, const float* tail, int tail_rows,
+                                const int* token_seq, const int* qsl, const int* slot_ids, void* out, int out_dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (taps < 1 || (taps > 1 && !tail)) TTIE_FAIL("stream_conv: %d taps need state rows", taps);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = C % 4 == 0 && !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)tail) & 15);
+    const dim3 grid(ceil_div(vec ? C / 4 : C, 128), T < 65535 ? T : 65535);
+#define SC(TO, V) TTIE_LAUNCH((stream_conv_kernel<TO, V>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out)
+    if (out_dtype == kF32) { if (vec) SC(float, 4); else SC(float, 1); }
+    else if (out_dtype == kBF16) { if (vec) SC(__nv_bfloat16, 4); else SC(__nv_bfloat16, 1); }
+    else TTIE_FAIL("stream_conv: unknown dtype %d", out_dtype);
+#undef SC
+    TTIE_CHECK_LAUNCH("stream_conv");
     return 0;
 }
 

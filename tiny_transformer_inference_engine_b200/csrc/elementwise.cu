@@ -509,21 +509,26 @@ extern "C" int ttie_rope_store_partial(const float* part, int S, long long part_
 
 // ------------------------------------------------------------------------------------------ rope + store, vectorised
 // Per step (not per layer): cos and sin of pos * inv_freq[j] for every token, [T][D/2] float2.
+// magnitude: what both cosine and sine are multiplied by (1 for a plain rotation; rescaled frequencies may come with one).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float2* __restrict__ cs,
-                                  int half, int total) {
+                                  int half, int total, float magnitude) {
     TTIE_PDL_ENTRY();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int t = i / half, j = i - t * half;
     float sn, c;
     sincosf((float)positions[t] * inv_freq[j], &sn, &c);
-    cs[i] = make_float2(c, sn);
+    cs[i] = make_float2(c * magnitude, sn * magnitude);
 }
 
+extern "C" int ttie_rope_table_scaled(const int* positions, const float* inv_freq, void* cs, int T, int half, float magnitude, void* stream);
 extern "C" int ttie_rope_table(const int* positions, const float* inv_freq, void* cs, int T, int half, void* stream) {
+    return ttie_rope_table_scaled(positions, inv_freq, cs, T, half, 1.0f, stream);
+}
+extern "C" int ttie_rope_table_scaled(const int* positions, const float* inv_freq, void* cs, int T, int half, float magnitude, void* stream) {
     if (T <= 0) return 0;
     const int total = T * half;
-    TTIE_LAUNCH(rope_table_kernel, ceil_div(total, 256), 256, 0, (cudaStream_t)stream, positions, inv_freq, (float2*)cs, half, total);
+    TTIE_LAUNCH(rope_table_kernel, ceil_div(total, 256), 256, 0, (cudaStream_t)stream, positions, inv_freq, (float2*)cs, half, total, magnitude);
     TTIE_CHECK_LAUNCH("rope_table");
     return 0;
 }

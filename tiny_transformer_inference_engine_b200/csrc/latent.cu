@@ -5,7 +5,8 @@
 //   latent_store:  proj[t, col0 : col0 + rank + rot]  ->  page row (RMS norm with weight on the first `rank`, rotation of
 //                  the last `rot` by the token's position), all in 32-bit, rounded once when stored
 //   latent_query:  per head [folded query (rank) | rotated query part (rot) | zeros] in the attention kernels' layout
-//   gate_heads:    out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h])
+//   gate_heads:    out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h]), or with a gate per value sigmoid(gate[t, h * vdim + j])
+//   rmsnorm_cols:  out[t, :] = proj[t, col0 : col0 + width] / rms * weight (a query latent between its two projections), 32-bit inside
 #include "common.cuh"
 using namespace ttie;
 
@@ -41,6 +42,21 @@ latent_store_kernel(const T* __restrict__ proj, long long ld, int col0, int T_, 
     for (int i = rank + rot + lane; i < width; i += 32) dst[i] = from_f32<T>(0.f);
 }
 
+// one warp per token: columns col0 .. col0 + width of a projected row over their root mean square, times a weight
+template <typename T, typename W>
+__global__ void __launch_bounds__(128)
+rmsnorm_cols_kernel(const T* __restrict__ proj, long long ld, int col0, int T_, int width, const W* __restrict__ w, float eps, T* __restrict__ out) {
+    TTIE_PDL_ENTRY();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T_) return;
+    const T* src = proj + (size_t)t * ld + col0;
+    float sq = 0.f;
+    for (int i = lane; i < width; i += 32) { const float v = to_f32(src[i]); sq = fmaf(v, v, sq); }
+    sq = warp_sum(sq);
+    const float r = 1.0f / sqrtf(sq / (float)width + eps);
+    for (int i = lane; i < width; i += 32) out[(size_t)t * width + i] = from_f32<T>(to_f32(src[i]) * r * to_f32(w[i]));
+}
+
 // q [T, H * (dim + rot)] (row stride ld), folded [H, T, rank] -> out [T, H, width]
 template <typename T>
 __global__ void latent_query_kernel(const T* __restrict__ q, long long ld, const T* __restrict__ folded, int T_, int H, int dim,
@@ -68,7 +84,7 @@ __global__ void latent_query_kernel(const T* __restrict__ q, long long ld, const
 
 // v [H, T, vdim]; gate logits gate[t * ld + h]; out [T, H * vdim]
 template <typename T>
-__global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__ gate, long long ld, int T_, int H, int vdim,
+__global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__ gate, long long ld, int per_value, int T_, int H, int vdim,
                                   T* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const int per_row = H * vdim;
@@ -77,7 +93,7 @@ __global__ void gate_heads_kernel(const T* __restrict__ v, const T* __restrict__
     const int h = col / vdim, j = col - h * vdim;
     for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
         const size_t e = t * per_row + col;
-        const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * ld + h])));
+        const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * ld + (per_value ? col : h)])));
         out[e] = from_f32<T>(to_f32(v[((size_t)h * T_ + t) * vdim + j]) * g);
     }
 }
@@ -120,16 +136,31 @@ __global__ void latent_query_vec8_kernel(const __nv_bfloat16* __restrict__ q, lo
     }
 }
 
-__global__ void gate_heads_vec8_kernel(const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ gate, long long ld, int T_, int H,
-                                       int vdim, __nv_bfloat16* __restrict__ out) {
+__global__ void gate_heads_vec8_kernel(const __nv_bfloat16* __restrict__ v, const __nv_bfloat16* __restrict__ gate, long long ld, int per_value,
+                                       int T_, int H, int vdim, __nv_bfloat16* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const int per_row = H * vdim;
     const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (col >= per_row) return;
     const int h = col / vdim, j = col - h * vdim;
     for (size_t t = blockIdx.y; t < (size_t)T_; t += gridDim.y) {
+        const uint4 x = *reinterpret_cast<const uint4*>(v + ((size_t)h * T_ + t) * vdim + j);
+        if (per_value) {                                             // (the gate row is 16-byte aligned like the others: the caller checks)
+            const uint4 gv = *reinterpret_cast<const uint4*>(gate + t * ld + col);
+            const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&x);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+            uint4 y;
+            __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&y);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(a[i]), g = __bfloat1622float2(g2[i]);
+                b[i] = __floats2bfloat162_rn(f.x / (1.0f + expf(-g.x)), f.y / (1.0f + expf(-g.y)));
+            }
+            *reinterpret_cast<uint4*>(out + t * per_row + col) = y;
+            continue;
+        }
         const float g = 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ld + h])));
-        *reinterpret_cast<uint4*>(out + t * per_row + col) = scale8(*reinterpret_cast<const uint4*>(v + ((size_t)h * T_ + t) * vdim + j), g);
+        *reinterpret_cast<uint4*>(out + t * per_row + col) = scale8(x, g);
     }
 }
 
@@ -154,6 +185,21 @@ extern "C" int ttie_latent_store(const void* proj, long long ld, int col0, int T
     return 0;
 }
 
+extern "C" int ttie_rmsnorm_cols(const void* proj, long long ld, int col0, int T, int width, const void* w, int w_dtype, float eps, void* out,
+                                 int dtype, void* stream) {
+    if (T <= 0) return 0;
+    if (width <= 0) TTIE_FAIL("rmsnorm_cols: width %d", width);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = ceil_div(T, 4);
+#define RC(TT, WW) TTIE_LAUNCH((rmsnorm_cols_kernel<TT, WW>), grid, 128, 0, s, (const TT*)proj, ld, col0, T, width, (const WW*)w, eps, (TT*)out)
+    if (dtype == kF32) { if (w_dtype != kF32) TTIE_FAIL("rmsnorm_cols: a 32-bit run needs 32-bit norm weights"); RC(float, float); }
+    else if (w_dtype == kF32) RC(__nv_bfloat16, float);
+    else RC(__nv_bfloat16, __nv_bfloat16);
+#undef RC
+    TTIE_CHECK_LAUNCH("rmsnorm_cols");
+    return 0;
+}
+
 extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded, int T, int H, int dim, int rank, int rot, int width,
                                  const void* cs, void* out, int dtype, void* stream) {
     if (T <= 0) return 0;
@@ -172,18 +218,19 @@ extern "C" int ttie_latent_query(const void* q, long long ld, const void* folded
     return 0;
 }
 
-extern "C" int ttie_gate_heads(const void* v, const void* gate, long long ld, int T, int H, int vdim, void* out, int dtype, void* stream) {
+extern "C" int ttie_gate_heads(const void* v, const void* gate, long long ld, int per_value, int T, int H, int vdim, void* out, int dtype,
+                               void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == kBF16 && vdim % 8 == 0 && aligned16(v) && aligned16(out)) {
+    if (dtype == kBF16 && vdim % 8 == 0 && aligned16(v) && aligned16(out) && !(per_value && (!aligned16(gate) || ld % 8))) {
         const dim3 g8(ceil_div(H * vdim / 8, 128), T < 65535 ? T : 65535);
-        TTIE_LAUNCH(gate_heads_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);
+        TTIE_LAUNCH(gate_heads_vec8_kernel, g8, 128, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, per_value, T, H, vdim, (__nv_bfloat16*)out);
         TTIE_CHECK_LAUNCH("gate_heads");
         return 0;
     }
     const dim3 grid(ceil_div(H * vdim, 256), T < 65535 ? T : 65535);
-    if (dtype == kF32) TTIE_LAUNCH(gate_heads_kernel<float>, grid, 256, 0, s, (const float*)v, (const float*)gate, ld, T, H, vdim, (float*)out);
-    else TTIE_LAUNCH(gate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, T, H, vdim, (__nv_bfloat16*)out);
+    if (dtype == kF32) TTIE_LAUNCH(gate_heads_kernel<float>, grid, 256, 0, s, (const float*)v, (const float*)gate, ld, per_value, T, H, vdim, (float*)out);
+    else TTIE_LAUNCH(gate_heads_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)v, (const __nv_bfloat16*)gate, ld, per_value, T, H, vdim, (__nv_bfloat16*)out);
     TTIE_CHECK_LAUNCH("gate_heads");
     return 0;
 }

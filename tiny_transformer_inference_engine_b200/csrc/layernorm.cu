@@ -5,6 +5,9 @@
 // model's last norm at the places whose logits are wanted).  The sum, both moments and the affine step are
 // 32-bit; the variance is the mean of the squared deviations (two passes over the row held in shared memory).
 // delta: none, [R, d] in the compute dtype or in 32-bit, or 32-bit partial sums [S, R, d] of a K-split product.
+// add_normed (layers that norm a sub-layer's output, not its input): the moments are those of delta alone and the stream
+// takes the normed delta on top of what it holds,  x <- x + (delta - mean(delta)) / sqrt(var(delta) + eps) * w + b;  the
+// copy in the compute dtype is of the new x.  A layer scale is folded into w by the caller.
 #include "common.cuh"
 using namespace ttie;
 
@@ -15,7 +18,7 @@ __global__ void __launch_bounds__(256)
 scale_add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
                            long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
                            const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
-                           int write_resid) {
+                           int write_resid, int add_normed) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     TTIE_PDL_ENTRY();
@@ -24,7 +27,7 @@ scale_add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delt
     float* x = resid + src * d;
     float sum = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = alpha * x[i];
+        float v = add_normed ? 0.f : alpha * x[i];
         if (delta) v += to_f32(delta[src * d + i]);
         for (int s = 0; s < S; ++s) v += dpart[(size_t)s * part_stride + src * d + i];     // fixed order
         row[i] = v;
@@ -35,7 +38,8 @@ scale_add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delt
     for (int i = threadIdx.x; i < d; i += blockDim.x) { const float c = row[i] - mean; sq += c * c; }
     const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)d + eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float y = (row[i] - mean) * rstd * to_f32(weight[i]) + (bias ? to_f32(bias[i]) : 0.f);
+        float y = (row[i] - mean) * rstd * to_f32(weight[i]) + (bias ? to_f32(bias[i]) : 0.f);
+        if (add_normed) y += x[i];
         if (write_resid) x[i] = y;
         if (out) out[(size_t)r * d + i] = from_f32<T>(y);
         if (out32) out32[(size_t)r * d + i] = y;
@@ -49,19 +53,19 @@ __global__ void __launch_bounds__(1024)
 scale_add_layernorm_reg_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
                                long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
                                const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
-                               int write_resid) {
+                               int write_resid, int add_normed) {
     __shared__ float scratch[32];
     TTIE_PDL_ENTRY();
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* x = resid + src * d;
-    float v[PER], w[PER], b[PER];
+    float v[PER], w[PER], b[PER], keep[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
-        v[j] = 0.f; w[j] = 0.f; b[j] = 0.f;
+        v[j] = 0.f; w[j] = 0.f; b[j] = 0.f; keep[j] = 0.f;
         if (i < d) {
-            v[j] = alpha * x[i];
+            if (add_normed) keep[j] = x[i]; else v[j] = alpha * x[i];
             if (delta) v[j] += to_f32(delta[src * d + i]);
             w[j] = to_f32(weight[i]);
             b[j] = bias ? to_f32(bias[i]) : 0.f;
@@ -85,7 +89,7 @@ scale_add_layernorm_reg_kernel(float* __restrict__ resid, const T* __restrict__ 
     for (int j = 0; j < PER; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i >= d) continue;
-        const float y = (v[j] - mean) * rstd * w[j] + b[j];
+        const float y = (v[j] - mean) * rstd * w[j] + b[j] + keep[j];
         if (write_resid) x[i] = y;
         if (out) out[(size_t)r * d + i] = from_f32<T>(y);
         if (out32) out32[(size_t)r * d + i] = y;
@@ -112,21 +116,21 @@ __global__ void __launch_bounds__(1024)
 scale_add_layernorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta, const float* __restrict__ dpart, int S,
                                long long part_stride, const int* __restrict__ rows, const W* __restrict__ weight,
                                const W* __restrict__ bias, T* __restrict__ out, float* __restrict__ out32, int d, float alpha, float eps,
-                               int write_resid) {
+                               int write_resid, int add_normed) {
     constexpr int PER = 2;
     __shared__ float scratch[32];
     TTIE_PDL_ENTRY();
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* x = resid + src * d;
-    float4 v[PER], w[PER], b[PER];
+    float4 v[PER], w[PER], b[PER], keep[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * 4;
-        v[j] = w[j] = b[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        v[j] = w[j] = b[j] = keep[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < d) {
             const float4 xv = ld4(x + i);
-            v[j] = make_float4(alpha * xv.x, alpha * xv.y, alpha * xv.z, alpha * xv.w);
+            if (add_normed) keep[j] = xv; else v[j] = make_float4(alpha * xv.x, alpha * xv.y, alpha * xv.z, alpha * xv.w);
             if (delta) { const float4 dv = ld4(delta + src * d + i); v[j].x += dv.x; v[j].y += dv.y; v[j].z += dv.z; v[j].w += dv.w; }
             w[j] = ld4(weight + i);
             if (bias) b[j] = ld4(bias + i);
@@ -154,8 +158,8 @@ scale_add_layernorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ 
     for (int j = 0; j < PER; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * 4;
         if (i >= d) continue;
-        const float4 y = make_float4((v[j].x - mean) * rstd * w[j].x + b[j].x, (v[j].y - mean) * rstd * w[j].y + b[j].y,
-                                     (v[j].z - mean) * rstd * w[j].z + b[j].z, (v[j].w - mean) * rstd * w[j].w + b[j].w);
+        const float4 y = make_float4((v[j].x - mean) * rstd * w[j].x + b[j].x + keep[j].x, (v[j].y - mean) * rstd * w[j].y + b[j].y + keep[j].y,
+                                     (v[j].z - mean) * rstd * w[j].z + b[j].z + keep[j].z, (v[j].w - mean) * rstd * w[j].w + b[j].w + keep[j].w);
         if (write_resid) st4(x + i, y);
         if (out) st4(out + (size_t)r * d + i, y);
         if (out32) st4(out32 + (size_t)r * d + i, y);
@@ -170,24 +174,24 @@ __global__ void cast_rows_kernel(const float* __restrict__ in, T* __restrict__ o
 
 template <typename T, typename W>
 int launch_ln(float* resid, const void* delta, const float* dpart, int S, long long part_stride, const int* rows, const void* w,
-              const void* b, void* out, float* out32, int R, int d, float alpha, float eps, int write_resid, cudaStream_t s) {
+              const void* b, void* out, float* out32, int R, int d, float alpha, float eps, int write_resid, int add_normed, cudaStream_t s) {
     const uintptr_t all = (uintptr_t)resid | (uintptr_t)delta | (uintptr_t)dpart | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out | (uintptr_t)out32;
     if (d % 4 == 0 && d <= 8 * 1024 && (all & 15) == 0 && part_stride % 4 == 0) {
         const int threads = ((d / 8 + 31) / 32) * 32 < 32 ? 32 : ((d / 8 + 31) / 32) * 32;
         TTIE_LAUNCH((scale_add_layernorm_vec_kernel<T, W>), R, threads, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows,
-                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid, add_normed);
         TTIE_CHECK_LAUNCH("scale_add_layernorm");
         return 0;
     }
     if (d <= 8 * 1024) {
         const int threads = d <= 1024 ? 128 : d <= 2048 ? 256 : d <= 4096 ? 512 : 1024;
         TTIE_LAUNCH((scale_add_layernorm_reg_kernel<T, W, 8>), R, threads, 0, s, resid, (const T*)delta, dpart, S, part_stride, rows,
-                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+                    (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid, add_normed);
         TTIE_CHECK_LAUNCH("scale_add_layernorm");
         return 0;
     }
     TTIE_LAUNCH((scale_add_layernorm_kernel<T, W>), R, 256, (size_t)d * sizeof(float), s, resid, (const T*)delta, dpart, S, part_stride, rows,
-                (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid);
+                (const W*)w, (const W*)b, (T*)out, out32, d, alpha, eps, write_resid, add_normed);
     TTIE_CHECK_LAUNCH("scale_add_layernorm");
     return 0;
 }
@@ -196,7 +200,7 @@ int launch_ln(float* resid, const void* delta, const float* dpart, int S, long l
 // delta_dtype: the dtype code of `delta` (ignored if null); out_dtype: of `out`; w_dtype: of weight and bias.
 extern "C" int ttie_scale_add_layernorm(float* resid, const void* delta, int delta_dtype, const float* dpart, int S, long long part_stride,
                                         const int* rows, const void* weight, const void* bias, int w_dtype, void* out, int out_dtype,
-                                        int R, int d, float alpha, float eps, int write_resid, void* stream) {
+                                        int R, int d, float alpha, float eps, int write_resid, int add_normed, void* stream) {
     if (R <= 0) return 0;
     if (d <= 0 || (size_t)d * sizeof(float) > 200 * 1024) TTIE_FAIL("layernorm: width %d not supported", d);
     cudaStream_t s = (cudaStream_t)stream;
@@ -215,11 +219,11 @@ extern "C" int ttie_scale_add_layernorm(float* resid, const void* delta, int del
     if (delta && delta_dtype != out_dtype) TTIE_FAIL("layernorm: delta dtype %d with output dtype %d", delta_dtype, out_dtype);
     if (out_dtype == kF32) {
         if (w_dtype != kF32) TTIE_FAIL("layernorm: a 32-bit run needs 32-bit norm weights");
-        return launch_ln<float, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, nullptr, (float*)out, R, d, alpha, eps, write_resid, s);
+        return launch_ln<float, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, nullptr, (float*)out, R, d, alpha, eps, write_resid, add_normed, s);
     }
     if (w_dtype == kF32)
-        return launch_ln<__nv_bfloat16, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, s);
-    return launch_ln<__nv_bfloat16, __nv_bfloat16>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, s);
+        return launch_ln<__nv_bfloat16, float>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, add_normed, s);
+    return launch_ln<__nv_bfloat16, __nv_bfloat16>(resid, delta, dpart, S, part_stride, rows, weight, bias, out, nullptr, R, d, alpha, eps, write_resid, add_normed, s);
 }
 
 extern "C" int ttie_cast_rows(const float* in, void* out, long long n, int out_dtype, void* stream) {

@@ -160,12 +160,23 @@ moe_plan_kernel(const int* __restrict__ idx, int P, int E, int tile_experts, int
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
+// An activation behind an ungated product, with the row's routing weight ahead of it: out = f(scale[row] * acc).  Scaling the
+// product is scaling the expert's input (the product is linear), done in 32-bit.  act 0: none, 1: the square of relu.
+// scale null: 1; scale_of (pair_of_pos) maps a sorted row to its (token, choice) pair, whose weight scale[] holds.
+struct RowAct { int act; const float* scale; const int* scale_of; };
+__device__ __forceinline__ float row_scale_of(const RowAct& ra, int pos) { return ra.scale ? ra.scale[ra.scale_of ? ra.scale_of[pos] : pos] : 1.0f; }
+__device__ __forceinline__ float row_act(const RowAct& ra, float v, float scale) {
+    v *= scale;
+    if (ra.act == 1) { v = fmaxf(v, 0.f); v *= v; }
+    return v;
+}
+
 // A rows: row_of[pos] / row_div (row_of null: pos itself).  W: [E, N, K] with expert stride.  C [P, N].
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 grouped_gemm_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ row_of, int row_div, const T* __restrict__ W,
                     long long w_stride, long long ldw, TO* __restrict__ C, long long ldc, const int* __restrict__ tiles,
-                    const int* __restrict__ meta, int N, int K) {
+                    const int* __restrict__ meta, int N, int K, RowAct ra) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     __shared__ int arow[BM];
@@ -211,10 +222,11 @@ grouped_gemm_kernel(const T* __restrict__ A, long long lda, const int* __restric
     for (int i = 0; i < TM; ++i) {
         const int r = ty * TM + i;
         if (r >= rows) continue;
+        const float rs = row_scale_of(ra, r0 + r);
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int gn = n0 + tx * TN + j;
-            if (gn < N) C[(size_t)(r0 + r) * ldc + gn] = from_f32<TO>(acc[i][j]);
+            if (gn < N) C[(size_t)(r0 + r) * ldc + gn] = from_f32<TO>(row_act(ra, acc[i][j], rs));
         }
     }
 }
@@ -240,7 +252,7 @@ template <typename T, typename TO, int MT>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 grouped_gemv_kernel(const T* __restrict__ A, long long lda, const int* __restrict__ row_of, int row_div, const T* __restrict__ W,
                     long long w_stride, long long ldw, TO* __restrict__ C, long long ldc, const int* __restrict__ tiles,
-                    const int* __restrict__ meta, int N, int K, GluConst glu) {
+                    const int* __restrict__ meta, int N, int K, GluConst glu, RowAct ra) {
     constexpr int VN = VecOf<T>::N;
     TTIE_PDL_ENTRY();
     const int tile = blockIdx.y;
@@ -300,8 +312,35 @@ grouped_gemv_kernel(const T* __restrict__ A, long long lda, const int* __restric
             for (int m = 0; m < MT; ++m)
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; ++r)
-                    if (m0 + m < rows && n0 + r < N) C[(size_t)(r0 + m0 + m) * ldc + n0 + r] = from_f32<TO>(acc[m][r]);
+                    if (m0 + m < rows && n0 + r < N)
+                        C[(size_t)(r0 + m0 + m) * ldc + n0 + r] = from_f32<TO>(row_act(ra, acc[m][r], row_scale_of(ra, r0 + m0 + m)));
         }
+    }
+}
+
+// in place over rows sorted by expert: x[pos, :] = f(scale * x[pos, :]) (behind a library product, which has no epilogue)
+template <typename T>
+__global__ void row_scale_act_kernel(T* __restrict__ x, long long ld, int rows, int F, RowAct ra) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)rows * F;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / F;
+        T* p = x + r * ld + (e - r * F);
+        *p = from_f32<T>(row_act(ra, to_f32(*p), row_scale_of(ra, (int)r)));
+    }
+}
+__global__ void row_scale_act_vec8_kernel(__nv_bfloat16* __restrict__ x, long long ld, int rows, int F8, RowAct ra) {
+    TTIE_PDL_ENTRY();
+    const size_t total = (size_t)rows * F8;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / F8;
+        uint4* p = reinterpret_cast<uint4*>(x + r * ld + (e - r * F8) * 8);
+        const float rs = row_scale_of(ra, (int)r);
+        uint4 v = *p;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); h[i] = __floats2bfloat162_rn(row_act(ra, f.x, rs), row_act(ra, f.y, rs)); }
+        *p = v;
     }
 }
 
@@ -320,7 +359,8 @@ __global__ void gather_rows_kernel(const T* __restrict__ x, long long ldx, const
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
                                    const T* __restrict__ shared, int T_, int d, int top, float* __restrict__ out,
-                                   const int* __restrict__ idx, int first_identity, const T* __restrict__ x, long long ldx) {
+                                   const int* __restrict__ idx, int first_identity, const T* __restrict__ x, long long ldx,
+                                   const float* __restrict__ shared_gate, long long ld_gate) {
     TTIE_PDL_ENTRY();
     const size_t total = (size_t)T_ * d;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
@@ -329,9 +369,9 @@ __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restri
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const bool same = idx && idx[t * top + k] >= first_identity;       // an identity expert: its output is the token's own row
-            acc = fmaf(wts[t * top + k], same ? to_f32(x[t * ldx + i]) : to_f32(Y[(size_t)pos_of_pair[t * top + k] * d + i]), acc);
+            acc = fmaf(wts ? wts[t * top + k] : 1.0f, same ? to_f32(x[t * ldx + i]) : to_f32(Y[(size_t)pos_of_pair[t * top + k] * d + i]), acc);
         }
-        if (shared) acc += to_f32(shared[e]);
+        if (shared) acc += to_f32(shared[e]) * (shared_gate ? 1.0f / (1.0f + expf(-shared_gate[t * ld_gate])) : 1.0f);
         out[e] = acc;
     }
 }
@@ -339,7 +379,8 @@ __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int* __restri
 // bfloat16 expert rows and shared rows, eight values per thread (d a multiple of 8)
 __global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
                                         const __nv_bfloat16* __restrict__ shared, int T_, int d8, int top, float* __restrict__ out,
-                                        const int* __restrict__ idx, int first_identity, const __nv_bfloat16* __restrict__ x, long long ldx) {
+                                        const int* __restrict__ idx, int first_identity, const __nv_bfloat16* __restrict__ x, long long ldx,
+                                        const float* __restrict__ shared_gate, long long ld_gate) {
     TTIE_PDL_ENTRY();
     const size_t total = (size_t)T_ * d8;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
@@ -349,7 +390,7 @@ __global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, con
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int k = 0; k < top; ++k) {
-            const float w = wts[t * top + k];
+            const float w = wts ? wts[t * top + k] : 1.0f;
             const bool same = idx && idx[t * top + k] >= first_identity;
             const uint4 v = *reinterpret_cast<const uint4*>(same ? x + t * ldx + i : Y + (size_t)pos_of_pair[t * top + k] * d8 * 8 + i);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -359,8 +400,9 @@ __global__ void moe_combine_vec8_kernel(const __nv_bfloat16* __restrict__ Y, con
         if (shared) {
             const uint4 v = *reinterpret_cast<const uint4*>(shared + t * d8 * 8 + i);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float sg = shared_gate ? 1.0f / (1.0f + expf(-shared_gate[t * ld_gate])) : 1.0f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); acc[2 * j] = fmaf(sg, f.x, acc[2 * j]); acc[2 * j + 1] = fmaf(sg, f.y, acc[2 * j + 1]); }
         }
         float* o = out + t * d8 * 8 + i;
         *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -413,11 +455,27 @@ extern "C" int ttie_moe_plan(const int* idx, int P, int E, int tile_experts, int
     return 0;
 }
 
+// act, row_scale, scale_of: an activation behind an ungated product, see RowAct (act 0 and row_scale null: the plain product)
+extern "C" int ttie_grouped_gemm_act(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
+                                     long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
+                                     int dtype, int out_dtype, int few_rows, int glu_F, float glu_alpha, float glu_limit, float glu_shift,
+                                     int act, const float* row_scale, const int* scale_of, void* stream);
+
 extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
                                  long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
                                  int dtype, int out_dtype, int few_rows, int glu_F, float glu_alpha, float glu_limit, float glu_shift,
                                  void* stream) {
+    return ttie_grouped_gemm_act(A, lda, row_of, row_div, W, w_stride, ldw, C, ldc, tiles, meta, max_tiles, N, K, dtype, out_dtype, few_rows,
+                                 glu_F, glu_alpha, glu_limit, glu_shift, 0, nullptr, nullptr, stream);
+}
+
+extern "C" int ttie_grouped_gemm_act(const void* A, long long lda, const int* row_of, int row_div, const void* W, long long w_stride,
+                                     long long ldw, void* C, long long ldc, const int* tiles, const int* meta, int max_tiles, int N, int K,
+                                     int dtype, int out_dtype, int few_rows, int glu_F, float glu_alpha, float glu_limit, float glu_shift,
+                                     int act, const float* row_scale, const int* scale_of, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
+    if (act < 0 || act > 1 || (glu_F > 0 && (act || row_scale))) TTIE_FAIL("grouped_gemm: activation %d (with a gated epilogue of width %d)", act, glu_F);
+    const RowAct ra{act, row_scale, scale_of};
     if (max_tiles > 65535) TTIE_FAIL("grouped_gemm: %d row tiles in one launch", max_tiles);
     cudaStream_t s = (cudaStream_t)stream;
     const int vn = dtype == kF32 ? 4 : 8, esz = dtype == kF32 ? 4 : 2;
@@ -426,7 +484,7 @@ extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of
         const GluConst glu{glu_F, glu_alpha, glu_limit, glu_shift};
         const dim3 g(glu_F > 0 ? ceil_div(glu_F, GV_WARPS * GV_ROWS / 2) : ceil_div(N, GV_WARPS * GV_ROWS), max_tiles);
 #define GV(TT, TO) TTIE_LAUNCH((grouped_gemv_kernel<TT, TO, 4>), g, GV_WARPS * 32, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
-                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K, glu)
+                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K, glu, ra)
         if (dtype == kF32 && out_dtype == kF32) GV(float, float);
         else if (dtype == kBF16 && out_dtype == kBF16) GV(__nv_bfloat16, __nv_bfloat16);
         else if (dtype == kBF16 && out_dtype == kF32) GV(__nv_bfloat16, float);
@@ -438,7 +496,7 @@ extern "C" int ttie_grouped_gemm(const void* A, long long lda, const int* row_of
     if (glu_F > 0) TTIE_FAIL("grouped_gemm: the gated epilogue exists in the few-rows form only");
     const dim3 grid(ceil_div(N, BN), max_tiles);
 #define GG(TT, TO) TTIE_LAUNCH((grouped_gemm_kernel<TT, TO>), grid, 256, 0, s, (const TT*)A, lda, row_of, row_div > 0 ? row_div : 1, (const TT*)W, \
-                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K)
+                               w_stride, ldw, (TO*)C, ldc, tiles, meta, N, K, ra)
     if (dtype == kF32 && out_dtype == kF32) GG(float, float);
     else if (dtype == kBF16 && out_dtype == kBF16) GG(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == kBF16 && out_dtype == kF32) GG(__nv_bfloat16, float);
@@ -460,8 +518,35 @@ extern "C" int ttie_gather_rows(const void* x, long long ldx, const int* row_of,
 
 // idx, first_identity, x, ldx: the choices, the first identity expert and the tokens' own rows (compute dtype, row stride ldx);
 // idx null: no identity experts
+// wts null: every chosen expert's row counts once (its weight went in ahead of the expert); shared_gate: 32-bit logits, one per token
+// ld_gate apart, whose sigmoid scales the shared expert's row (null: 1)
+extern "C" int ttie_moe_combine_gated(const void* Y, int y_dtype, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
+                                      float* out, int dtype, const int* idx, int first_identity, const void* x, long long ldx,
+                                      const float* shared_gate, long long ld_gate, void* stream);
+
 extern "C" int ttie_moe_combine(const void* Y, int y_dtype, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
                                 float* out, int dtype, const int* idx, int first_identity, const void* x, long long ldx, void* stream) {
+    return ttie_moe_combine_gated(Y, y_dtype, pos_of_pair, wts, shared, T, d, top, out, dtype, idx, first_identity, x, ldx, nullptr, 0, stream);
+}
+
+extern "C" int ttie_row_scale_act(void* x, long long ld, int rows, int F, int act, const float* row_scale, const int* scale_of, int dtype,
+                                  void* stream) {
+    if (rows <= 0 || F <= 0) return 0;
+    if (act < 0 || act > 1) TTIE_FAIL("row_scale_act: activation %d", act);
+    const RowAct ra{act, row_scale, scale_of};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == kBF16 && F % 8 == 0 && ld % 8 == 0 && !((uintptr_t)x & 15))
+        TTIE_LAUNCH(row_scale_act_vec8_kernel, grid_for((size_t)rows * F / 8), 256, 0, s, (__nv_bfloat16*)x, ld, rows, F / 8, ra);
+    else if (dtype == kBF16) TTIE_LAUNCH(row_scale_act_kernel<__nv_bfloat16>, grid_for((size_t)rows * F), 256, 0, s, (__nv_bfloat16*)x, ld, rows, F, ra);
+    else if (dtype == kF32) TTIE_LAUNCH(row_scale_act_kernel<float>, grid_for((size_t)rows * F), 256, 0, s, (float*)x, ld, rows, F, ra);
+    else TTIE_FAIL("row_scale_act: unknown dtype %d", dtype);
+    TTIE_CHECK_LAUNCH("row_scale_act");
+    return 0;
+}
+
+extern "C" int ttie_moe_combine_gated(const void* Y, int y_dtype, const int* pos_of_pair, const float* wts, const void* shared, int T, int d, int top,
+                                      float* out, int dtype, const int* idx, int first_identity, const void* x, long long ldx,
+                                      const float* shared_gate, long long ld_gate, void* stream) {
     if (T <= 0) return 0;
     if (idx && !x) TTIE_FAIL("moe_combine: identity experts need the tokens' own rows");
     const size_t total = (size_t)T * d;
@@ -469,13 +554,13 @@ extern "C" int ttie_moe_combine(const void* Y, int y_dtype, const int* pos_of_pa
     if (dtype == kBF16 && y_dtype == kBF16 && d % 8 == 0 && ((((uintptr_t)Y) | ((uintptr_t)shared) | ((uintptr_t)out)) & 15) == 0
         && !(idx && ((((uintptr_t)x) & 15) || ldx % 8))) {
         TTIE_LAUNCH(moe_combine_vec8_kernel, grid_for(total / 8), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d / 8, top, out,
-                    idx, first_identity, (const __nv_bfloat16*)x, ldx);
+                    idx, first_identity, (const __nv_bfloat16*)x, ldx, shared_gate, ld_gate);
         TTIE_CHECK_LAUNCH("moe_combine");
         return 0;
     }
-    if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out, idx, first_identity, (const float*)x, ldx);
-    else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx);
-    else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx);
+    if (dtype == kF32 && y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<float, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const float*)shared, T, d, top, out, idx, first_identity, (const float*)x, ldx, shared_gate, ld_gate);
+    else if (y_dtype == kF32) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, float>), grid_for(total), 256, 0, s, (const float*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx, shared_gate, ld_gate);
+    else if (dtype == kBF16) TTIE_LAUNCH((moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>), grid_for(total), 256, 0, s, (const __nv_bfloat16*)Y, pos_of_pair, wts, (const __nv_bfloat16*)shared, T, d, top, out, idx, first_identity, (const __nv_bfloat16*)x, ldx, shared_gate, ld_gate);
     else TTIE_FAIL("moe_combine: expert rows of dtype %d beside a shared expert of dtype %d", y_dtype, dtype);
     TTIE_CHECK_LAUNCH("moe_combine");
     return 0;

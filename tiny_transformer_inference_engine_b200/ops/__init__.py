@@ -31,6 +31,7 @@ _SIGNATURES = {
     "ttie_rope_store_partial": [_c_void, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int,
                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_rope_table": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ttie_rope_table_scaled": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_void],
     "ttie_rope_store_vec": [_c_void, _c_ll, _c_void, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void,
                             _c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_skinny_gemm": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -50,18 +51,25 @@ _SIGNATURES = {
     "ttie_paged_attention_mma_form": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
                                       _c_void, _c_int, _c_void],
+    "ttie_paged_attention_weights": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
+                                     _c_void, _c_int, _c_int, _c_void, _c_void],
+    "ttie_paged_attention_mma_weights": [_c_void, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int,
+                                         _c_void, _c_int, _c_int, _c_void, _c_void],
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int,
                                 _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_tc_pair": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_scale_add_layernorm": [_c_void, _c_void, _c_int, _c_void, _c_int, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
-                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_void],
     "ttie_cast_rows": [_c_void, _c_void, _c_ll, _c_int, _c_void],
     "ttie_latent_store": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_float, _c_void, _c_void, _c_void,
                           _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_latent_query": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
-    "ttie_gate_heads": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_gate_heads": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ttie_rmsnorm_cols": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_int, _c_float, _c_void, _c_int, _c_void],
     "ttie_gemm_f32_batched": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_void],
     "ttie_causal_conv": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void,
                          _c_void, _c_void, _c_void, _c_int, _c_void],
@@ -73,12 +81,19 @@ _SIGNATURES = {
     "ttie_moe_plan": [_c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void],
     "ttie_grouped_gemm": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
+    "ttie_grouped_gemm_act": [_c_void, _c_ll, _c_void, _c_int, _c_void, _c_ll, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_int, _c_int, _c_int,
+                              _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void, _c_void, _c_void],
+    "ttie_row_scale_act": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
+    "ttie_moe_combine_gated": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int, _c_void, _c_ll,
+                               _c_void, _c_ll, _c_void],
     "ttie_skinny_gemm_glu": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void],
     "ttie_gather_rows": [_c_void, _c_ll, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_moe_combine": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int, _c_void, _c_ll, _c_void],
     "ttie_qkv_conv_rope_store": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void,
-                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_float, _c_int, _c_float, _c_int,
+                                 _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_float, _c_void, _c_int, _c_float, _c_int,
                                  _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ttie_proj_row_rms": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_void, _c_int, _c_void],
+    "ttie_stream_conv": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
     "ttie_conv_tail_update": [_c_void, _c_ll, _c_int, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_token_shift_mix": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int,
@@ -549,11 +564,12 @@ class CudaOps:
         self._check(self.lib.ttie_swiglu(_ptr(gate_up), _ptr(out), T, F, self._dt(out), self._stream(out)), "swiglu")
         self.launches += 1
 
-    def rope_table(self, positions, inv_freq):
-        """cos and sin of pos * inv_freq for every token of the step: float32 [T, D/2, 2]."""
+    def rope_table(self, positions, inv_freq, magnitude=1.0):
+        """cos and sin of pos * inv_freq for every token of the step, both times ``magnitude``: float32 [T, D/2, 2]."""
         T, half = positions.shape[0], inv_freq.shape[0]
         cs = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
-        self._check(self.lib.ttie_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cs), T, half, self._stream(cs)), "rope_table")
+        self._check(self.lib.ttie_rope_table_scaled(_ptr(positions), _ptr(inv_freq), _ptr(cs), T, half, float(magnitude), self._stream(cs)),
+                    "rope_table")
         self.launches += 1
         return cs
 
@@ -589,13 +605,15 @@ class CudaOps:
                                                  stream), "rope_store")
         self.launches += 1
 
-    def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size=None):
+    def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size=None,
+                       tile_loop_only=False):
         """Which attention kernel runs and how the key range is split: (kernel, num_splits,
         split_len).  bfloat16 with a head size that is a multiple of 16 up to 128, or 256, runs
         on tensor cores; everything else runs the general float32-arithmetic kernel.  The key
         range is split only when the query rows alone cannot fill the GPU.  Every layer of a step
-        asks the same question, so the answers are kept."""
-        key = (dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+        asks the same question, so the answers are kept.  ``tile_loop_only``: the choice is between the ``mma.sync`` tile loop
+        and the general kernel (weights that only those two compute)."""
+        key = (dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, bool(tile_loop_only))
         plan = self._plans.get(key)
         if plan is None:
             if len(self._plans) >= 4096:
@@ -603,9 +621,11 @@ class CudaOps:
             plan = self._plans[key] = self._attention_plan(*key)
         return plan
 
-    def _attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size):
+    def _attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, tile_loop_only=False):
         G = num_heads // num_kv_heads
         rows = max_q_len * G
+        if tile_loop_only:
+            page_size = None                                         # (no tcgen05 kernel, whose page sizes would matter)
         if (dtype == torch.bfloat16 and page_size is not None and head_dim > 128
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len, max_q_len)
@@ -630,10 +650,10 @@ class CudaOps:
             # per kv head, head size 64 or 128) - since it stages only the rows in use and sets itself up while its
             # predecessor finishes it is ahead of the decode form at every context (8 requests x 32 heads: 7.1 against
             # 10.7 us at 100 keys, 8.8 against 10.6 at 1,024, 9.6 against 10.7 at 2,048) -, else the decode form
-            plan = self._tc_split_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+            plan = None if tile_loop_only else self._tc_split_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
             if plan is not None:
                 return plan
-            plan = self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
+            plan = None if tile_loop_only else self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:
                 return plan
             kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
@@ -798,18 +818,25 @@ class CudaOps:
 
     def paged_attention(self, qkv, num_heads, num_kv_heads, head_dim, k_pages, v_pages, block_table, page_size,
                         query_start_loc, seq_lens, num_seqs, max_q_len, max_kv_len, scale, window, out,
-                        plan=None, softcap=0.0, chunk=0):
+                        plan=None, softcap=0.0, chunk=0, weights="softmax", head_bias=None):
         """Causal attention of the step's query rows over the paged keys and values.  ``window`` > 0: a row at position p
         sees keys p - window + 1 .. p.  ``chunk`` > 0 (instead of a window): a row at position p sees the keys of its own
         chunk of ``chunk`` positions up to p, chunks counted from position 0 of the sequence.  ``softcap`` > 0: a score s
-        (scale applied) becomes softcap * tanh(s / softcap) before mask and softmax."""
+        (scale applied) becomes softcap * tanh(s / softcap) before mask and softmax.  ``weights`` "sigmoid": a visible key
+        weighs sigmoid(score + head_bias[head]) (``head_bias`` float32 [num_heads] or None) and nothing is normalised over the
+        keys; such steps run the general kernel or the ``mma.sync`` tile loop."""
+        if weights not in ("softmax", "sigmoid"):
+            raise KernelError(f"paged_attention: unknown kind of weights {weights!r}")
+        sig = weights == "sigmoid"
         if chunk and window:
             raise KernelError("paged_attention: a window and a chunk size exclude each other")
         T = qkv.shape[0]
         if max_kv_len > block_table.shape[1] * page_size:
             raise KernelError(f"paged_attention: a block table of {block_table.shape[1]} pages of {page_size} keys cannot cover {max_kv_len} keys")
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
-            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, None if sig else page_size, sig)
+        if sig and kernel not in ("mma", "simt"):
+            raise KernelError(f"paged_attention: sigmoid weights have no {kernel!r} kernel")
         if kernel in ("tc", "tcpp"):
             scratch = None
             if num_splits > 1:
@@ -826,26 +853,30 @@ class CudaOps:
         if num_splits > 1 and not form:
             scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
         if form is not None:
-            self._check(self.lib.ttie_paged_attention_mma_form(
+            self._check(self.lib.ttie_paged_attention_mma_weights(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
                 head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
-                form, self._stream(qkv)), "paged_attention_mma")
+                form, 1 if sig else 0, _ptr(head_bias), self._stream(qkv)), "paged_attention_mma")
             self.launches += 2 if (num_splits > 1 and not form) else 1
             return
         else:
-            self._check(self.lib.ttie_paged_attention(
+            self._check(self.lib.ttie_paged_attention_weights(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
                 page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads, num_kv_heads,
                 head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
-                self._dt(qkv), self._stream(qkv)), "paged_attention")
+                self._dt(qkv), 1 if sig else 0, _ptr(head_bias), self._stream(qkv)), "paged_attention")
         self.launches += 2 if num_splits > 1 else 1
 
     # ---- post-norm layers
-    def scale_add_layernorm(self, resid, delta, alpha, weight, bias, eps, out=None, rows=None, num_rows=None, write_resid=True):
+    def scale_add_layernorm(self, resid, delta, alpha, weight, bias, eps, out=None, rows=None, num_rows=None, write_resid=True,
+                            add_normed=False):
         """resid <- LayerNorm(alpha * resid + delta) * weight + bias over the 32-bit stream [R, d]; ``out`` (compute dtype, or
         None) receives a copy.  ``delta``: None, [R, d] or float32 partial sums [S, R, d].  With ``rows`` the rows are gathered
-        into ``out`` [num_rows, d]."""
+        into ``out`` [num_rows, d].  ``add_normed``: resid <- resid + LayerNorm(delta) * weight + bias instead (the norm sits on a
+        sub-layer's output; ``alpha`` is not used)."""
+        if add_normed and (delta is None or rows is not None):
+            raise KernelError("scale_add_layernorm: add_normed needs a delta and takes no row list")
         d = resid.shape[1]
         R = resid.shape[0] if rows is None else int(num_rows)
         dp, pp, S, stride, ddt = None, None, 0, 0, 0
@@ -857,7 +888,8 @@ class CudaOps:
         odt = self._dt(out) if out is not None else (0 if weight.dtype == torch.float32 and (delta is None or delta.dtype == torch.float32) else 1)
         self._check(self.lib.ttie_scale_add_layernorm(_ptr(resid), dp, ddt, pp, S, stride, _ptr(rows), _ptr(weight), _ptr(bias),
                                                       self._dt(weight), _ptr(out), odt, R, d, float(alpha), float(eps),
-                                                      1 if (write_resid and rows is None) else 0, self._stream(resid)),
+                                                      1 if (write_resid and rows is None) else 0, 1 if add_normed else 0,
+                                                      self._stream(resid)),
                     "scale_add_layernorm")
         self.launches += 1
 
@@ -889,12 +921,35 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def gate_heads(self, v, gate, num_heads, vdim):
-        """out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h]); v [H, T, vdim], gate a view [T, H] with a row stride."""
+    def gate_heads(self, v, gate, num_heads, vdim, per_value=False):
+        """out[t, h, :] = v[h, t, :] * sigmoid(gate[t, h]); v [H, T, vdim], gate a view [T, H] with a row stride.
+        ``per_value``: gate is [T, H * vdim], one number per value."""
         T = gate.shape[0]
         out = torch.empty((T, num_heads * vdim), dtype=v.dtype, device=v.device)
-        self._check(self.lib.ttie_gate_heads(_ptr(v), _ptr(gate), gate.stride(0), T, num_heads, vdim, _ptr(out), self._dt(v),
-                                             self._stream(v)), "gate_heads")
+        self._check(self.lib.ttie_gate_heads(_ptr(v), _ptr(gate), gate.stride(0), 1 if per_value else 0, T, num_heads, vdim, _ptr(out),
+                                             self._dt(v), self._stream(v)), "gate_heads")
+        self.launches += 1
+        return out
+
+    def rmsnorm_cols(self, proj, col0, width, weight, eps):
+        """out[t] = proj[t, col0 : col0 + width] / sqrt(mean(.^2) + eps) * weight, [T, width] in proj's dtype (32-bit inside)."""
+        T = proj.shape[0]
+        out = torch.empty((T, width), dtype=proj.dtype, device=proj.device)
+        self._check(self.lib.ttie_rmsnorm_cols(_ptr(proj), proj.stride(0), int(col0), T, int(width), _ptr(weight), self._dt(weight),
+                                               float(eps), _ptr(out), self._dt(proj), self._stream(proj)), "rmsnorm_cols")
+        self.launches += 1
+        return out
+
+    # ---- a causal convolution over time on the rows of the 32-bit residual stream
+    def stream_conv(self, resid, conv_w, taps, tail, token_seq, query_start_loc, slot_ids, dtype):
+        """h[t] = sum_k conv_w[k] * x_(t - taps + 1 + k) per channel over the stream rows ``resid`` float32 [T, d]; ``conv_w``
+        float32 tap-major [taps, d]; rows before the step come from ``tail`` float32 [slots + 1, taps - 1, d] (None with one
+        tap).  Returns h [T, d] in ``dtype``.  ``conv_tail_update`` (given ``resid``) advances the state rows afterwards."""
+        T, d = resid.shape
+        out = torch.empty((T, d), dtype=dtype, device=resid.device)
+        self._check(self.lib.ttie_stream_conv(_ptr(resid), T, d, int(taps), _ptr(conv_w), _ptr(tail), 0 if tail is None else tail.shape[0],
+                                              _ptr(token_seq), _ptr(query_start_loc), _ptr(slot_ids), _ptr(out), _DT[dtype],
+                                              self._stream(resid)), "stream_conv")
         self.launches += 1
         return out
 
@@ -953,7 +1008,7 @@ class CudaOps:
     # ---- attention with a short convolution on its projections, partial rotation, another value size, gated heads
     def qkv_conv_rope_store(self, proj, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, taps, conv_w, tail, positions, token_seq,
                             query_start_loc, slot_ids, cs_table, rot, style, k_pages, v_pages, block_table, page_size, write_kv,
-                            norm_w=None, norm_eps=0.0, v_from_k=False, q_temp=None):
+                            norm_w=None, norm_eps=0.0, v_from_k=False, q_temp=None, row_inv=None):
         """From a step's projected rows ``proj`` [T, >= Hq*D + Hkv*D + Hkv*Dv] (columns [q | k | v]): the short causal
         convolution over time (``conv_w`` float32 tap-major [taps, channels]; ``tail`` float32 state rows
         [slots + 1, taps - 1, channels] with each request's last projected rows; ``taps`` 1 and ``conv_w`` None: none), the
@@ -963,18 +1018,29 @@ class CudaOps:
         is divided by its root mean square (``norm_eps`` inside the root) and multiplied by its weights, before the rotation.
         ``v_from_k``: ``proj`` has no v columns and a value head is its key head as it stands before norm and rotation.
         ``q_temp`` (coef, every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+        ``row_inv`` (float32 [T, 2] from ``proj_row_rms``): one norm over the whole q and one over the whole k projection
+        instead of one per head; ``norm_w`` is then float32 [Hq*D + Hkv*D], a weight per channel.
         Returns q [T, Hq * padded_dim].  The state rows are advanced by ``conv_tail_update``."""
         T = proj.shape[0]
         q = torch.empty((T, num_heads * padded_dim), dtype=proj.dtype, device=proj.device)
         self._check(self.lib.ttie_qkv_conv_rope_store(
             _ptr(proj), proj.stride(0), T, num_heads, num_kv_heads, head_dim, v_dim, padded_dim, int(taps), _ptr(conv_w), _ptr(tail),
             0 if tail is None else tail.shape[0], _ptr(positions), _ptr(token_seq), _ptr(query_start_loc), _ptr(slot_ids),
-            _ptr(cs_table), int(rot), int(style), _ptr(norm_w), float(norm_eps), 1 if v_from_k else 0,
+            _ptr(cs_table), int(rot), int(style), _ptr(norm_w), float(norm_eps), _ptr(row_inv), 1 if v_from_k else 0,
             float(q_temp[0]) if q_temp else 0.0, int(q_temp[1]) if q_temp else 0,
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             int(page_size), k_pages.shape[0], 1 if write_kv else 0, self._dt(proj), self._stream(proj)), "qkv_conv_rope_store")
         self.launches += 1
         return q
+
+    def proj_row_rms(self, proj, nq, nk, eps):
+        """float32 [T, 2]: 1 / sqrt(mean(x^2) + eps) over the first ``nq`` columns of every row of ``proj`` and over the next ``nk``."""
+        T = proj.shape[0]
+        inv = torch.empty((T, 2), dtype=torch.float32, device=proj.device)
+        self._check(self.lib.ttie_proj_row_rms(_ptr(proj), proj.stride(0), T, int(nq), int(nk), float(eps), _ptr(inv), self._dt(proj),
+                                               self._stream(proj)), "proj_row_rms")
+        self.launches += 1
+        return inv
 
     def conv_tail_update(self, proj, channels, taps, tail, query_start_loc, slot_ids, num_seqs):
         """Moves the last ``taps - 1`` projected rows of every request of the step into its state row (oldest first)."""
@@ -1251,6 +1317,35 @@ class CudaOps:
             return out
         return self.glu(self.grouped_linear(x, w_gu, plan, gather_div), hidden, alpha, limit, shift)
 
+    _ROW_ACTS = {None: 0, "relu2": 1}
+
+    def grouped_act(self, x, w_up, plan, gather_div, act, row_scale=None):
+        """The experts' up products over rows sorted by expert, with an activation behind them: row ``pos`` is
+        ``act(s * (x[pair_of_pos[pos] // gather_div] @ w_up[e].T))`` -> [pairs, F] in the compute dtype.  ``row_scale`` float32
+        [T, top]: s is the pair's routing weight - the weight goes in AHEAD of the expert (it multiplies the expert's input; the
+        product being linear, it is applied to the 32-bit sums) -, None: 1.  ``act``: "relu2" or None.  Few rows, or 32-bit: the
+        activation is the product's epilogue; many rows in bfloat16: the library's grouped product, then one pass in place."""
+        E, N, K = w_up.shape
+        code = self._ROW_ACTS[act]
+        few = plan["pairs"] <= self.grouped_few_rows
+        scale_of = plan["pair_of_pos"] if row_scale is not None else None
+        if not few and x.dtype == torch.bfloat16:
+            out = self._library_grouped(x, w_up, plan, gather_div)
+            if out is not None:
+                if code or row_scale is not None:
+                    self._check(self.lib.ttie_row_scale_act(_ptr(out), out.stride(0), plan["pairs"], N, code, _ptr(row_scale), _ptr(scale_of),
+                                                            self._dt(out), self._stream(out)), "row_scale_act")
+                    self.launches += 1
+                return out
+        out = torch.empty((plan["pairs"], N), dtype=x.dtype, device=x.device)
+        self._check(self.lib.ttie_grouped_gemm_act(_ptr(x), x.stride(0), _ptr(plan["pair_of_pos"]) if gather_div else None, int(gather_div),
+                                                   _ptr(w_up), w_up.stride(0), w_up.stride(1), _ptr(out), N, _ptr(plan["tiles"]),
+                                                   _ptr(plan["meta"]), plan["max_tiles"], N, K, self._dt(x), self._dt(out), 1 if few else 0,
+                                                   0, 1.0, 0.0, 0.0, code, _ptr(row_scale), _ptr(scale_of), self._stream(x)),
+                    "grouped_gemm (activation)")
+        self.launches += 1
+        return out
+
     def grouped_linear(self, x, w, plan, gather_div=0, out_dtype=None):
         """Rows sorted by expert times their expert's matrix: w [E, N, K]; row ``pos`` of the result is
         x[pair_of_pos[pos] // gather_div] @ w[e].T (``gather_div`` 0: x[pos]).  Few rows: a kernel that streams each tile's
@@ -1270,18 +1365,23 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def moe_combine(self, y, plan, wts, shared, num_tokens, dim, x=None):
+    def moe_combine(self, y, plan, wts, shared, num_tokens, dim, x=None, shared_gate=None):
         """float32 [T, d]: the weighted sum of each token's expert rows (+ the shared expert's output).  ``x`` [T, d] (compute
-        dtype): the tokens' own rows, which an identity expert returns (a plan made with ``identity`` > 0 needs them)."""
+        dtype): the tokens' own rows, which an identity expert returns (a plan made with ``identity`` > 0 needs them).
+        ``wts`` None: the rows are added as they are (their weights went in ahead of the experts).  ``shared_gate``: float32
+        logits, one per token (a view with a row stride), whose sigmoid scales the shared expert's row."""
         out = torch.empty((num_tokens, dim), dtype=torch.float32, device=y.device)
-        top = wts.shape[1]
+        top = plan["idx"].shape[1]
         sdt = self._dt(shared) if shared is not None else self._dt(x) if x is not None else self._dt(y)
         identity = plan["real_experts"] < plan["offsets"].numel() - 1
         if identity and x is None:
             raise KernelError("moe_combine: identity experts return the tokens' own rows, which were not given")
-        self._check(self.lib.ttie_moe_combine(_ptr(y), self._dt(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim,
-                                              top, _ptr(out), sdt, _ptr(plan["idx"]) if identity else None, plan["real_experts"],
-                                              _ptr(x) if identity else None, x.stride(0) if identity else 0, self._stream(y)),
+        if shared_gate is not None and (shared is None or shared_gate.dtype != torch.float32):
+            raise KernelError("moe_combine: a gate on the shared expert needs that expert's rows and 32-bit logits")
+        self._check(self.lib.ttie_moe_combine_gated(_ptr(y), self._dt(y), _ptr(plan["pos_of_pair"]), _ptr(wts), _ptr(shared), num_tokens, dim,
+                                                    top, _ptr(out), sdt, _ptr(plan["idx"]) if identity else None, plan["real_experts"],
+                                                    _ptr(x) if identity else None, x.stride(0) if identity else 0, _ptr(shared_gate),
+                                                    0 if shared_gate is None else shared_gate.stride(0), self._stream(y)),
                     "moe_combine")
         self.launches += 1
         return out

@@ -26,7 +26,12 @@ value with ``sigmoid(W_g x)``, ``W_g`` as large as ``W_q`` would be at the value
 only), ``qk_norm`` (its eps: every query and key head is divided by its root mean square and multiplied by a weight of
 ``head_dim`` values that all heads share, ``<q><norm_suffix>`` and ``<k><norm_suffix>``, before the rotation), ``v_from_k``
 (there is no value projection: a value head is its key head as projected, before norm and rotation), ``q_temp``
-(``coef``, ``every``: the query at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``).  The general step: one product
+(``coef``, ``every``: the query at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``),
+``qk_norm_over="projection"`` (with ``qk_norm``: ONE root mean square over all of a token's q and one over all of its k, before
+they are cut into heads, and a weight per channel, ``<q><norm_suffix>`` of ``heads * head_dim`` values and ``<k><norm_suffix>`` of
+``kv_heads * head_dim``; the default ``"head"`` is the norm per head above), ``weights="sigmoid"`` (no softmax: a visible key
+weighs ``sigmoid(score + b_h)`` and the weights are not normalised over the keys; ``head_bias`` names the tensor of one ``b``
+per head, None: no bias).  The general step: one product
 ``[W_q; W_k; W_v; W_g] x``; one kernel convolves, normalises, rotates, writes q and stores k and v - rows padded with zeros to
 ``padded_dim``, a multiple of 16 that holds both sizes, so every attention kernel of the package applies; a second moves the
 convolution's inputs into the state row; attention; the gate kernel drops the padding; ``W_o``.
@@ -51,7 +56,8 @@ class PagedAttention(Mixer):
                  v_head_dim: Optional[int] = None, conv_taps: Optional[int] = None, softcap: Optional[float] = None,
                  gated=False, qkv_bias: bool = False, weight_suffix: str = ".weight", bias_suffix: str = ".bias",
                  conv_suffix: str = ".conv", chunk: Optional[int] = None, qk_norm: Optional[float] = None,
-                 norm_suffix: str = ".norm", v_from_k: bool = False, q_temp: Optional[Dict[str, float]] = None):
+                 norm_suffix: str = ".norm", v_from_k: bool = False, q_temp: Optional[Dict[str, float]] = None,
+                 qk_norm_over: str = "head", weights: str = "softmax", head_bias: Optional[str] = None):
         super().__init__(prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
@@ -83,6 +89,16 @@ class PagedAttention(Mixer):
         self.gate_per_value = gated == "value"
         self.weight_suffix, self.bias_suffix, self.conv_suffix, self.norm_suffix = weight_suffix, bias_suffix, conv_suffix, norm_suffix
         self.qk_norm = None if qk_norm is None else float(qk_norm)
+        if qk_norm_over not in ("head", "projection"):
+            raise ValueError(f"qk_norm_over must be 'head' or 'projection', got {qk_norm_over!r}")
+        self.norm_whole = self.qk_norm is not None and qk_norm_over == "projection"
+        if self.norm_whole and conv_taps is not None:
+            raise ValueError("a norm over the whole projection and a convolution on it exclude each other")
+        if weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"weights must be 'softmax' or 'sigmoid', got {weights!r}")
+        if head_bias is not None and weights != "sigmoid":
+            raise ValueError("a bias per head belongs to sigmoid weights (a softmax does not see it)")
+        self.weights, self.head_bias_name, self.head_bias = weights, head_bias, None
         self.v_from_k = bool(v_from_k)
         if self.v_from_k and self.v_head_dim != head_dim:
             raise ValueError(f"values that are the keys have the keys' size {head_dim}, not {self.v_head_dim}")
@@ -96,7 +112,7 @@ class PagedAttention(Mixer):
             raise ValueError(f"the position encoding rotates {self.rot_dim} values of a head of {head_dim}")
         self.general = (self.v_head_dim != head_dim or self.has_conv or self.gated or self.qkv_bias
                         or self.rot_dim not in (0, head_dim) or self.qk_norm is not None or self.v_from_k
-                        or self.q_temp is not None)
+                        or self.q_temp is not None or self.weights != "softmax")
         if self.general and (self.shares_kv or self.bias):
             raise ValueError("the general attention step has neither a shared cache nor an output bias")
         self.padded_dim = -(-max(head_dim, self.v_head_dim) // 16) * 16 if self.general else head_dim
@@ -136,7 +152,9 @@ class PagedAttention(Mixer):
                 specs[f"{n[key]}{self.conv_suffix}"] = ParamSpec((r, self.conv_taps), storage="vector", init="normal", std=0.5)
         if self.qk_norm is not None:
             for key in ("q", "k"):
-                specs[f"{n[key]}{self.norm_suffix}"] = ParamSpec((D,), storage="vector", init="ones")
+                specs[f"{n[key]}{self.norm_suffix}"] = ParamSpec((rows[key] if self.norm_whole else D,), storage="vector", init="ones")
+        if self.head_bias_name is not None:
+            specs[self.head_bias_name] = ParamSpec((self.num_heads,), storage="vector", init="normal", std=0.5)
         if self.gated:
             specs[f"{n['g']}{ws}"] = ParamSpec((self.num_heads * (Dv if self.gate_per_value else 1), d))
         return specs
@@ -156,7 +174,10 @@ class PagedAttention(Mixer):
             w = torch.cat([params[f"{n[k]}{self.conv_suffix}"].float() for k in qkv], dim=0)
             self.conv_w = w.t().contiguous()
         if self.qk_norm is not None:                                    # 32-bit, the query heads' weights then the key heads'
-            self.norm_w = torch.stack([params[f"{n[k]}{self.norm_suffix}"].float() for k in ("q", "k")]).contiguous()
+            ws_ = [params[f"{n[k]}{self.norm_suffix}"].float() for k in ("q", "k")]
+            self.norm_w = (torch.cat(ws_) if self.norm_whole else torch.stack(ws_)).contiguous()
+        if self.head_bias_name is not None:
+            self.head_bias = params[self.head_bias_name].float().contiguous()
 
     def load(self, params):
         if self.general:
@@ -195,10 +216,11 @@ class PagedAttention(Mixer):
         rot = self.rot_dim if inv_freq is not None else 0
         cs = self.position.step_table(ctx) if rot else None
         state = tail.state if tail is not None else None
+        row_inv = ops.proj_row_rms(proj, Hq * D, Hkv * D, self.qk_norm) if self.norm_whole else None
         q = ops.qkv_conv_rope_store(proj, Hq, Hkv, D, Dv, Dp, self.conv_taps, self.conv_w, state, ctx.positions, ctx.token_seq,
                                     ctx.query_start_loc, ctx.slot_ids, cs, rot, style, cache.k_pages, cache.v_pages,
                                     cache.block_table, cache.page_size, cache.writable, norm_w=self.norm_w,
-                                    norm_eps=self.qk_norm or 0.0, v_from_k=self.v_from_k, q_temp=self.q_temp)
+                                    norm_eps=self.qk_norm or 0.0, v_from_k=self.v_from_k, q_temp=self.q_temp, row_inv=row_inv)
         if self.conv_taps > 1 and tail.writable:
             ops.conv_tail_update(proj, C, self.conv_taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
         out = torch.empty((T, Hq * Dp), dtype=x.dtype, device=x.device)
@@ -215,7 +237,8 @@ class PagedAttention(Mixer):
             c = classes[0]
             ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
                                 c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
-                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0, chunk=self.chunk or 0)
+                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0, chunk=self.chunk or 0,
+                                weights=self.weights, head_bias=self.head_bias)
             return
         for ci, c in enumerate(classes):
             key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
@@ -225,7 +248,7 @@ class PagedAttention(Mixer):
             ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
                                 cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
                                 c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi], softcap=self.softcap or 0.0,
-                                chunk=self.chunk or 0)
+                                chunk=self.chunk or 0, weights=self.weights, head_bias=self.head_bias)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         tail = None

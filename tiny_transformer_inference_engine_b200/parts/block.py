@@ -8,7 +8,11 @@ feed-forward (``ffn`` None) has only the first sub-layer.
 """
 from __future__ import annotations
 
-from .base import Block, PartSpec, ResidualStream, StepContext, mixer_cache_argument
+from typing import Optional
+
+import torch
+
+from .base import Block, ParamSpec, PartSpec, FixedStateNeed, ResidualStream, StepContext, mixer_cache_argument
 from ..registry import register_part, build_part
 
 
@@ -69,4 +73,72 @@ class PostNormBlock(Block):
         if self.ffn is not None:
             f = self.ffn.forward(x, ctx)
             x = self.ffn_norm.scale_add_norm(stream.resid, f, self.alpha)
+        stream.x = x
+
+
+@register_part("block", "sublayer_norm")
+class SublayerNormBlock(Block):
+    """The norm sits on each sub-layer's OUTPUT: ``x = x + norm_a(mixer(x))`` followed by ``x = x + norm_b(ffn(x))``; the
+    sub-layers read the stream itself (a copy in the compute dtype that the norm kernel writes beside the 32-bit sum).  The
+    norm parts carry a layer scale if the design has one (``LayerNorm(scale=)``).  A layer without a feed-forward (``ffn``
+    None) ends after the first sum.
+
+    ``input_conv`` (``name``, ``taps``; None: none): what the mixer reads is ``x + conv(x)``, a causal convolution over time on
+    every channel, ``conv(x)_t = sum_j w[:, j] * x_(t - taps + 1 + j)`` with zeros before the sequence's start (tensor ``name``
+    [dim, taps]; tap ``taps - 1`` multiplies the current token).  The ``x`` itself is one more on the last tap, added in 32-bit
+    when the tensor is loaded; the kernel reads the 32-bit stream, and the last ``taps - 1`` stream rows of a request are kept
+    in a state row of this block (the first of its cache needs)."""
+
+    def __init__(self, prefix: str, dim: int, mixer: PartSpec, mixer_norm: PartSpec, ffn: PartSpec = None, ffn_norm: PartSpec = None,
+                 input_conv: Optional[dict] = None):
+        super().__init__(prefix)
+        self.dim = int(dim)
+        self.mixer = build_part("mixer", mixer)
+        self.mixer_norm = build_part("norm", mixer_norm)
+        self.ffn = build_part("ffn", ffn) if ffn is not None else None
+        self.ffn_norm = build_part("norm", ffn_norm) if ffn is not None else None
+        self.conv_name, self.taps = None, 0
+        if input_conv is not None:
+            self.conv_name, self.taps = input_conv["name"], int(input_conv["taps"])
+            if self.taps < 1:
+                raise ValueError(f"input_conv.taps must be >= 1, got {input_conv['taps']}")
+        self.conv_w = None
+
+    def children(self):
+        return [p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None]
+
+    def param_specs(self):
+        if self.conv_name is None:
+            return {}
+        return {self.conv_name: ParamSpec((self.dim, self.taps), storage="vector", init="normal", std=0.3)}
+
+    def load(self, params):
+        if self.conv_name is not None:                               # tap-major, 32-bit, the stream's own row on the last tap
+            w = params[self.conv_name].float().t().contiguous()
+            w[self.taps - 1] += 1.0
+            self.conv_w = w
+
+    def cache_needs(self):
+        own = [FixedStateNeed((self.taps - 1, self.dim), "float32")] if self.taps > 1 else []
+        return own + list(self.mixer.cache_needs())
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches) -> None:
+        if stream.delta is not None:
+            raise ValueError("a block that norms its sub-layers' outputs cannot follow a block that leaves a sum unformed")
+        ops, resid = self.ops, stream.resid
+        caches = list(caches)
+        if self.conv_name is not None:
+            tail = caches.pop(0) if self.taps > 1 else None
+            state = None if tail is None else tail.state
+            h = ops.stream_conv(resid, self.conv_w, self.taps, state, ctx.token_seq, ctx.query_start_loc, ctx.slot_ids, self.dtype)
+            if tail is not None and tail.writable:
+                ops.conv_tail_update(resid, self.dim, self.taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
+        else:
+            h = stream.x
+            if h is None:                                            # the first layer: the embedding's rows
+                h = resid if self.dtype == resid.dtype else ops.cast_rows(resid, self.dtype)
+        a = self.mixer.forward(h, ctx, mixer_cache_argument(self.mixer, caches))
+        x = self.mixer_norm.add_normed(resid, a)
+        if self.ffn is not None:
+            x = self.ffn_norm.add_normed(resid, self.ffn.forward(x, ctx))
         stream.x = x

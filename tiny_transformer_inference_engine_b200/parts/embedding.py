@@ -1,23 +1,28 @@
 """Token embedding and output head.
 
 Embedding (models/embedding.py:9-15): a row gather, no position term; the gathered row
-(times ``scale``, a parameter; the reference has none) starts the 32-bit residual sum.  Head (models/transformer_block.py:170,181):
+(times ``scale``, a parameter; the reference has none) starts the 32-bit residual sum.  ``norm``
+(a norm part's spec; the reference has none): the rows are normed in place before the first layer.  Head (models/transformer_block.py:170,181):
 ``logits = x @ W.T`` without bias, untied from the embedding; logits leave in 32-bit.
 """
 from __future__ import annotations
 
 import torch
 
-from .base import Embedding, Head, ParamSpec, StepContext
-from ..registry import register_part
+from .base import Embedding, Head, ParamSpec, PartSpec, StepContext
+from ..registry import register_part, build_part
 
 
 @register_part("embedding", "token")
 class TokenEmbedding(Embedding):
-    def __init__(self, prefix: str, vocab_size: int, dim: int, name: str = "weight", scale: float = 1.0):
+    def __init__(self, prefix: str, vocab_size: int, dim: int, name: str = "weight", scale: float = 1.0, norm: PartSpec = None):
         super().__init__(prefix)
         self.vocab_size, self.dim, self.name, self.scale = int(vocab_size), int(dim), name, float(scale)
+        self.norm = build_part("norm", norm) if norm is not None else None
         self.table = None
+
+    def children(self):
+        return [self.norm] if self.norm is not None else []
 
     def param_specs(self):
         return {self.name: ParamSpec((self.vocab_size, self.dim))}
@@ -28,6 +33,8 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx: StepContext) -> torch.Tensor:
         resid = torch.empty((ctx.num_tokens, self.dim), dtype=torch.float32, device=ctx.device)
         self.ops.embed(ctx.token_ids, self.table, resid, self.scale)
+        if self.norm is not None:
+            self.norm.norm_in_place(resid)
         return resid
 
 

@@ -111,6 +111,6 @@ class MLP(FeedForward):
     def product_weights(self):
         return [self.w_up, self.w_down]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, partial_ok: bool = True) -> torch.Tensor:
         act = self.ops.linear_act(x, self.w_up, self.act)             # [T, F]
-        return self.ops.linear(act, self.w_down, None, partial_ok=True)
+        return self.ops.linear(act, self.w_down, None, partial_ok=partial_ok)

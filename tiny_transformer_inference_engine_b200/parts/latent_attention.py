@@ -12,7 +12,11 @@ kernels' granule.  Softmax scale, window (keys ``pos - window + 1 .. pos``), rot
 nothing: its run entry reads the cache of the entry that owns one; ``cache_window`` is then the owner's need (the widest
 window among the layers that read the cache).
 
-One product ``[W_q; W_g; W_dkv] h`` feeds the step; the folds are batched per-head products.
+``q_rank`` (optional): the queries go through a latent of their own, ``c_q = rmsnorm(W_dq h) * w`` and ``q = W_uq c_q`` (tensors
+``dq``, ``dq.norm``, ``uq`` instead of ``q``).  ``gated="value"``: the gate is as wide as the concatenated heads,
+``sigmoid(W_g h)`` value by value (``True`` / ``"head"``: one number per head).
+
+One product ``[W_q (or W_dq); W_g; W_dkv] h`` feeds the step; the folds are batched per-head products.
 """
 from __future__ import annotations
 
@@ -29,9 +33,9 @@ ROW_GRANULE = 16            # cache rows are padded to a multiple of this (the t
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
     def __init__(self, prefix: str, d_model: int, num_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
-                 position: PartSpec, scale: float, eps: float, window: Optional[int] = None, gated: bool = True,
+                 position: PartSpec, scale: float, eps: float, window: Optional[int] = None, gated=True,
                  shares_kv: bool = False, cache_window: Optional[int] = None, page_size: Optional[int] = None,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, q_rank: Optional[int] = None):
         super().__init__(prefix)
         if rot_dim % 2:
             raise ValueError(f"rotated size {rot_dim} must be even")
@@ -39,15 +43,22 @@ class LatentAttention(Mixer):
             raise ValueError(f"window must be >= 1 or None, got {window}")
         self.d_model, self.num_heads, self.dim, self.rot_dim = int(d_model), int(num_heads), int(dim), int(rot_dim)
         self.vdim, self.kv_rank, self.scale, self.eps = int(vdim), int(kv_rank), float(scale), float(eps)
+        if gated not in (False, True, "head", "value"):
+            raise ValueError(f"gated must be False, True / 'head' or 'value', got {gated!r}")
         self.window, self.gated, self.shares_kv = window, bool(gated), bool(shares_kv)
+        self.gate_per_value = gated == "value"
+        self.q_rank = None if q_rank is None else int(q_rank)
+        if self.q_rank is not None and self.q_rank < 1:
+            raise ValueError(f"q_rank must be >= 1 or None, got {q_rank}")
         self.cache_window = cache_window if cache_window is not None else window
         self.page_size = None if page_size is None else int(page_size)
         self.row = -(-(self.kv_rank + self.rot_dim) // ROW_GRANULE) * ROW_GRANULE
         self.position = build_part("position", position)
-        self.names = {"q": "q", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "g": "g", "o": "o"}
+        self.names = {"q": "q", "dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
+                      "g": "g", "o": "o"}
         if names:
             self.names.update(names)
-        self.w_in = self.w_uk_t = self.w_uv = self.w_out = self.norm_w = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_out = self.norm_w = self.w_uq = self.q_norm_w = None
 
     def children(self):
         return [self.position]
@@ -55,12 +66,17 @@ class LatentAttention(Mixer):
     # ---------------------------------------------------------------- tensors
     def param_specs(self):
         n, d, H = self.names, self.d_model, self.num_heads
-        specs = {n["q"]: ParamSpec((H * (self.dim + self.rot_dim), d)),
-                 n["uk"]: ParamSpec((H * self.dim, self.kv_rank)),
+        specs = {n["uk"]: ParamSpec((H * self.dim, self.kv_rank)),
                  n["uv"]: ParamSpec((H * self.vdim, self.kv_rank)),
                  n["o"]: ParamSpec((d, H * self.vdim))}
+        if self.q_rank is None:
+            specs[n["q"]] = ParamSpec((H * (self.dim + self.rot_dim), d))
+        else:
+            specs[n["dq"]] = ParamSpec((self.q_rank, d))
+            specs[n["dq_norm"]] = ParamSpec((self.q_rank,), storage="vector", init="ones")
+            specs[n["uq"]] = ParamSpec((H * (self.dim + self.rot_dim), self.q_rank))
         if self.gated:
-            specs[n["g"]] = ParamSpec((H, d))
+            specs[n["g"]] = ParamSpec((H * self.vdim if self.gate_per_value else H, d))
         if not self.shares_kv:
             specs[n["dkv"]] = ParamSpec((self.kv_rank + self.rot_dim, d))
             specs[n["dkv_norm"]] = ParamSpec((self.kv_rank,), storage="vector", init="ones")
@@ -68,10 +84,15 @@ class LatentAttention(Mixer):
 
     def load(self, params):
         n, H = self.names, self.num_heads
-        mats = [params[n["q"]]] + ([params[n["g"]]] if self.gated else []) + ([] if self.shares_kv else [params[n["dkv"]]])
+        first = params[n["q"]] if self.q_rank is None else params[n["dq"]]
+        mats = [first] + ([params[n["g"]]] if self.gated else []) + ([] if self.shares_kv else [params[n["dkv"]]])
         self.w_in = torch.cat(mats, dim=0).contiguous()
-        self.col_g = H * (self.dim + self.rot_dim)
-        self.col_dkv = self.col_g + (H if self.gated else 0)
+        self.col_g = first.shape[0]
+        self.gate_cols = 0 if not self.gated else H * self.vdim if self.gate_per_value else H
+        self.col_dkv = self.col_g + self.gate_cols
+        if self.q_rank is not None:
+            self.w_uq = params[n["uq"]].contiguous()
+            self.q_norm_w = params[n["dq_norm"]]
         # W_uk^T per head: [H, rank, dim], so that folded[h] = q_n[h] @ w_uk_t[h].T
         self.w_uk_t = params[n["uk"]].view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = params[n["uv"]].view(H, self.vdim, self.kv_rank).contiguous()
@@ -79,7 +100,7 @@ class LatentAttention(Mixer):
         self.norm_w = None if self.shares_kv else params[n["dkv_norm"]]
 
     def product_weights(self):
-        return [self.w_in, self.w_out]
+        return [self.w_in, self.w_out] + ([self.w_uq] if self.w_uq is not None else [])
 
     def validate(self, ops, dtype, page_size):
         check = getattr(ops, "check_attention", None)
@@ -99,9 +120,13 @@ class LatentAttention(Mixer):
         if cache.writable and not self.shares_kv:
             ops.latent_store(proj, self.col_dkv, self.kv_rank, self.rot_dim, self.norm_w, self.eps, cs, ctx.positions,
                              ctx.token_seq, cache.k_pages, cache.block_table, cache.page_size)
-        qh = proj[:, :self.col_g].view(T, H, self.dim + self.rot_dim)
+        if self.q_rank is None:
+            qrows = proj                                             # (its first columns; the kernels take the row stride)
+        else:
+            qrows = ops.linear(ops.rmsnorm_cols(proj, 0, self.q_rank, self.q_norm_w, self.eps), self.w_uq, None)
+        qh = qrows[:, :H * (self.dim + self.rot_dim)].view(T, H, self.dim + self.rot_dim)
         folded = ops.batched_linear(qh[:, :, :self.dim].transpose(0, 1), self.w_uk_t)          # [H, T, rank]
-        q = ops.latent_query(proj, folded, H, self.dim, self.kv_rank, self.rot_dim, R, cs)
+        q = ops.latent_query(qrows, folded, H, self.dim, self.kv_rank, self.rot_dim, R, cs)
         out = torch.empty((T, H * R), dtype=x.dtype, device=x.device)
         classes = ctx.classes()
         if len(classes) == 1:
@@ -121,7 +146,7 @@ class LatentAttention(Mixer):
         lat = out.view(T, H, R)[:, :, :self.kv_rank].transpose(0, 1)                            # [H, T, rank], a view
         v = ops.batched_linear(lat, self.w_uv)                                                  # [H, T, vdim]
         if self.gated:
-            heads = ops.gate_heads(v, proj[:, self.col_g:self.col_g + H], H, self.vdim)
+            heads = ops.gate_heads(v, proj[:, self.col_g:self.col_g + self.gate_cols], H, self.vdim, per_value=self.gate_per_value)
         else:
             heads = v.transpose(0, 1).reshape(T, H * self.vdim)
         return ops.linear(heads, self.w_out, None, partial_ok=True)

@@ -18,6 +18,13 @@ sine and cosine of that product in 32-bit.
 ``l > original / low`` becomes ``f / factor``, and between the two ``s = (original / l - low) / (high - low)`` blends
 ``(1 - s) f / factor + s f``.  ``dim`` is the number of rotated values; a mixer may rotate only the first ``dim``
 values of a wider head.
+
+``scaling`` with ``kind: "yarn"`` (``factor``, ``original``, ``fast``, ``slow``) is YaRN's rescaling by pair index instead:
+with ``turn(t) = dim * ln(original / (2 pi t)) / (2 ln base)`` - the (fractional) pair index whose frequency makes ``t`` turns
+over ``original`` positions -, ``lo = max(floor(turn(fast)), 0)``, ``hi = min(ceil(turn(slow)), dim - 1)`` and
+``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair ``i`` turns at ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``; and
+cosine and sine are both multiplied by ``YARN_MAGNITUDE_SLOPE * ln(factor) + 1`` (so a product of two rotated vectors grows by
+its square).
 """
 from __future__ import annotations
 
@@ -29,6 +36,7 @@ from .base import PositionEncoding
 from ..registry import register_part
 
 ROTARY_STYLES = {"interleaved": 0, "half": 1}
+YARN_MAGNITUDE_SLOPE = 0.1
 
 
 @register_part("position", "rope")
@@ -41,7 +49,15 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"unknown rotary style {style!r}; known: {sorted(ROTARY_STYLES)}")
         self.dim, self.base, self.style = int(dim), float(base), style
         self.scaling = None
-        if scaling is not None:
+        self.yarn = None
+        if scaling is not None and scaling.get("kind") == "yarn":
+            missing = [k for k in ("factor", "original", "fast", "slow") if k not in scaling]
+            if missing:
+                raise ValueError(f"yarn scaling lacks {missing}")
+            self.yarn = {k: float(scaling[k]) for k in ("factor", "original", "fast", "slow")}
+            if min(self.yarn.values()) <= 0 or self.base == 1.0:
+                raise ValueError(f"yarn scaling {scaling!r}: needs positive constants and a base other than 1")
+        elif scaling is not None:
             missing = [k for k in ("factor", "low", "high", "original") if k not in scaling]
             if missing:
                 raise ValueError(f"rotary scaling lacks {missing}")
@@ -52,6 +68,18 @@ class RotaryEncoding(PositionEncoding):
 
     def frequencies(self) -> torch.Tensor:
         """float32 [dim / 2]: the rotation frequency of every pair."""
+        if self.yarn is not None:
+            y, out = self.yarn, []
+
+            def turn(t):
+                return self.dim * math.log(y["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+
+            lo, hi = max(math.floor(turn(y["fast"])), 0), min(math.ceil(turn(y["slow"])), self.dim - 1)
+            for i in range(self.dim // 2):                           # few values, once: in 64-bit, rounded at the end
+                f = self.base ** (-2.0 * i / self.dim)
+                ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                out.append(f / y["factor"] * ramp + f * (1.0 - ramp))
+            return torch.tensor(out, dtype=torch.float64).to(torch.float32)
         if self.scaling is None:
             return 1.0 / (self.base ** (torch.arange(0, self.dim, 2).float() / self.dim))
         sc, out = self.scaling, []
@@ -67,6 +95,11 @@ class RotaryEncoding(PositionEncoding):
                 out.append((1.0 - s) * f / sc["factor"] + s * f)
         return torch.tensor(out, dtype=torch.float64).to(torch.float32)
 
+    @property
+    def magnitude(self) -> float:
+        """What cosine and sine are multiplied by: 1 unless the frequencies are YaRN's."""
+        return 1.0 if self.yarn is None else YARN_MAGNITUDE_SLOPE * math.log(self.yarn["factor"]) + 1.0
+
     def bind(self, ops, dtype, device):
         super().bind(ops, dtype, device)
         self._inv_freq = self.frequencies().to(device=device, dtype=torch.float32).contiguous()
@@ -80,9 +113,13 @@ class RotaryEncoding(PositionEncoding):
         if not hasattr(self.ops, "rope_table"):
             return None
         tables = ctx.step_cache
-        key = ("rope_table", self.dim, self.base, None if self.scaling is None else tuple(sorted(self.scaling.items())))
+        key = ("rope_table", self.dim, self.base, None if self.scaling is None else tuple(sorted(self.scaling.items())),
+               None if self.yarn is None else tuple(sorted(self.yarn.items())))
         if key not in tables:
-            tables[key] = self.ops.rope_table(ctx.positions, self._inv_freq)
+            if self.yarn is None:
+                tables[key] = self.ops.rope_table(ctx.positions, self._inv_freq)
+            else:
+                tables[key] = self.ops.rope_table(ctx.positions, self._inv_freq, self.magnitude)
         return tables[key]
 
     def apply(self, q, k, positions):
