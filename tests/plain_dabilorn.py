@@ -96,8 +96,8 @@ def latent_attention(h, W, p, m, eps):
     q = (cq @ W[p + "uq"].T).view(S, H, D + R)
     dkv = h @ W[p + "dkv"].T
     c = rms_norm(dkv[:, :rank], eps) * W[p + "dkv.norm"]
-    k_rot = rotate(dkv[:, rank:].reshape(S, 1, R), m["rot"], "interleaved")[:, 0]
-    q_rot = rotate(q[:, :, D:].contiguous(), m["rot"], "interleaved")
+    k_rot = rotate(dkv[:, rank:].reshape(S, 1, R), m.get("rot"), "interleaved")[:, 0]
+    q_rot = rotate(q[:, :, D:].contiguous(), m.get("rot"), "interleaved")
     k_plain = (c @ W[p + "uk"].T).view(S, H, D)
     v = (c @ W[p + "uv"].T).view(S, H, Dv)
     mask = visible(S)
@@ -186,7 +186,7 @@ def forward(config, weights, tokens, after_layer=None):
     x = layer_norm(W["embed"][torch.as_tensor(tokens, dtype=torch.long)], W["embed.norm"], eps)
     for i, L in enumerate(config["layers"]):
         p = f"l{i}."
-        h = x + time_conv(x, W[p + "canon1"])
+        h = x + time_conv(x, W[p + "canon1"]) if config.get("canon") else x
         a = MIXERS[L["type"]](h, W, p + "mix.", L["mixer"], eps)
         x = x + layer_norm(a, W[p + "norm1"], eps) * W[p + "ls1"]
         if L.get("mlp") is not None:

@@ -88,7 +88,10 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int T_, int E, 
     } else {
         for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-logits[(size_t)t * ld + e]));
     }
-    for (int e = lane; e < E; e += 32) c[e] = correction ? s[e] + correction[e] : s[e];
+    // Sigmoid scores with nothing added and one group: the choice is made by the logits themselves.  The sigmoid is monotone, so
+    // the order is the scores' own - also where two large logits round to the same score in 32-bit, which exact arithmetic tells apart.
+    const bool by_logit = !softmax && !correction && groups == 1;
+    for (int e = lane; e < E; e += 32) c[e] = by_logit ? logits[(size_t)t * ld + e] : correction ? s[e] + correction[e] : s[e];
     __syncwarp();
     for (int g = lane; g < groups; g += 32) {                        // a group's rating: the sum of its `group_top` (1 or 2) highest values
         float b0 = -INFINITY, b1 = -INFINITY;

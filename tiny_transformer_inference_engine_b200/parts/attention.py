@@ -232,13 +232,13 @@ class PagedAttention(Mixer):
     def _attend(self, q, D, ctx, cache, out):
         """One attention launch per class of requests (decoded tokens; prompt portions), each planned as if it were alone."""
         ops, Hq, Hkv = self.ops, self.num_heads, self.num_kv_heads
+        extra = {} if self.weights == "softmax" else {"weights": self.weights, "head_bias": self.head_bias}
         classes = ctx.classes()
         if len(classes) == 1:
             c = classes[0]
             ops.paged_attention(q, Hq, Hkv, D, cache.k_pages, cache.v_pages, cache.block_table, cache.page_size,
                                 c.query_start_loc, ctx.seq_lens, ctx.num_seqs, c.max_q_len, c.max_kv_len,
-                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0, chunk=self.chunk or 0,
-                                weights=self.weights, head_bias=self.head_bias)
+                                self.scale, self.window or 0, out, softcap=self.softcap or 0.0, chunk=self.chunk or 0, **extra)
             return
         for ci, c in enumerate(classes):
             key = ("attention class views", id(cache.block_table), ci)    # the same for every layer of a cache group
@@ -248,7 +248,7 @@ class PagedAttention(Mixer):
             ops.paged_attention(q[c.tok_lo:c.tok_hi], Hq, Hkv, D, cache.k_pages, cache.v_pages, views[0],
                                 cache.page_size, c.query_start_loc, views[1], c.seq_hi - c.seq_lo, c.max_q_len,
                                 c.max_kv_len, self.scale, self.window or 0, out[c.tok_lo:c.tok_hi], softcap=self.softcap or 0.0,
-                                chunk=self.chunk or 0, weights=self.weights, head_bias=self.head_bias)
+                                chunk=self.chunk or 0, **extra)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
         tail = None
