@@ -330,8 +330,27 @@ def mokalorn_config(width, heads, layers=4):
             "logit_softcap": 30.0, "layers": out, "max_seq_len": 4096}
 
 
+def dabilorn_config(width, heads, layers=4):
+    """A Dabilorn model at layer sizes that resemble a real model's: latent attention with heads of 128 + 64 rotated values, a
+    256-value cache row (latent of 192), a query latent of 3/8 of the width and YaRN-rescaled frequencies; grouped-query attention
+    with sigmoid weights, heads of 128 (eight query heads per kv head), 64 rotated values and chunks of 1,024 positions; time
+    mixing with heads of 64 and a decay path of rank 64; four convolution taps in front of every mixer; feed-forwards of 16
+    experts of width / 2, four chosen, beside a gated shared expert of the model's width.  Layer order: time mixing, latent
+    attention, sigmoid attention, latent attention, repeated."""
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": 3 * width // 8, "scale": 192 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "mask": {"size": 1024},
+           "rot": {"base": 10000.0, "dims": 64}, "scale": 128 ** -0.5}
+    mix = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 4}, "shared": {"ff": width}}
+    kinds = (("wkv", mix), ("latent_attention", lat), ("attention", att), ("latent_attention", lat))
+    out = [{"type": kinds[i % 4][0], "mixer": dict(kinds[i % 4][1]), "mlp": moe} for i in range(layers)]
+    return {"architecture": "Dabilorn", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "layers": out,
+            "max_seq_len": 4096}
+
+
 DESIGNS = {"munevik": ("Munevik", munevik_config, 1024), "mizupel": ("Mizupel", mizupel_config, 1024),
-           "mokalorn": ("Mokalorn", mokalorn_config, 0)}     # name, configuration, window
+           "mokalorn": ("Mokalorn", mokalorn_config, 0), "dabilorn": ("Dabilorn", dabilorn_config, 0)}     # name, configuration, window
 
 
 def like_config(width, heads, layers=4):
@@ -347,7 +366,8 @@ class OpRecorder:
              "scale_add_layernorm", "cast_rows", "latent_store", "latent_query", "gate_heads", "batched_linear", "causal_conv",
              "rglru_scan", "glu", "linear_glu", "grouped_glu", "moe_route", "moe_plan", "grouped_linear", "moe_combine",
              "qkv_conv_rope_store", "conv_tail_update", "gate_head_rows", "token_shift_mix", "wkv_scan", "mlstm_scan", "head_norm_gate",
-             "activation", "linear_act", "wkv_decay", "mlstm_gates", "rotate_heads", "retention_scan")
+             "activation", "linear_act", "wkv_decay", "mlstm_gates", "rotate_heads", "retention_scan", "stream_conv", "proj_row_rms",
+             "rmsnorm_cols", "grouped_act")
 
     def __init__(self, ops):
         self.ops, self.calls, self.orig, self.depth = ops, [], {}, 0
@@ -425,7 +445,13 @@ def op_cost(name, args, kw, out, kv_lens, window):
     if name == "batched_linear":
         x, w = args[0], args[1]
         return _tensor_bytes([w, out]) + x.numel() * x.element_size(), 2 * x.shape[0] * x.shape[1] * w.shape[1] * w.shape[2]
-    if name in ("grouped_linear", "grouped_glu"):
+    if name == "stream_conv":                                      # (resid, weights, ...): the stream's rows read, the mixer's input written
+        return _tensor_bytes([args[0], out]), 0
+    if name == "proj_row_rms":                                     # (proj, nq, nk, eps): the q and k columns read
+        return args[0].shape[0] * (args[1] + args[2]) * args[0].element_size() + _tensor_bytes(out), 0
+    if name == "rmsnorm_cols":                                     # (proj, col0, width, ...)
+        return args[0].shape[0] * args[2] * args[0].element_size() + _tensor_bytes(out), 0
+    if name in ("grouped_linear", "grouped_glu", "grouped_act"):
         x, w, plan = args[0], args[1], args[2]
         rows = plan["pairs"]
         return _tensor_bytes([w, out]) + rows * w.shape[2] * x.element_size(), 2 * rows * w.shape[1] * w.shape[2]
@@ -477,7 +503,7 @@ def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
         else:
             ideal = max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops"] * 1e12)) * 1e6
         key = name
-        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu", "linear_glu", "grouped_glu", "linear_act"):
+        if name in ("linear", "batched_linear", "grouped_linear", "linear_swiglu", "linear_glu", "grouped_glu", "linear_act", "grouped_act"):
             w = args[1]
             key = f"{name} {list(w.shape)}"
         r = rows.setdefault(key, {"calls": 0, "us": 0.0, "ideal_us": 0.0})
@@ -489,8 +515,9 @@ def time_ops(eng, entries_fn, pk, kv_lens, window, iters=8):
 
 
 def run_design(args, pk):
-    """Prefill and decode throughput of a design (``--design``) at a few sizes, beside the closest existing model (multi-query
-    GPT) at equal width and depth, with every operation of a step timed alone against its roofline."""
+    """Prefill and decode throughput of a design (``--design``) at a few sizes, beside the closest existing model (``--beside``:
+    the multi-query GPT, or another design) at equal width and depth, with every operation of a step timed alone against its
+    roofline."""
     import torch
     from tiny_transformer_inference_engine_b200 import Engine, ModelConfig, EngineConfig, CacheConfig, SchedulerConfig, StepEntry, SamplingParams
     from tiny_transformer_inference_engine_b200.weights import random_tensors
@@ -499,7 +526,9 @@ def run_design(args, pk):
     report = {}
     for width, heads in sizes:
         design_name, design_config, design_window = DESIGNS[args.design]
-        for label, cfg in ((args.design, design_config(width, heads, args.layers or 4)), ("mqa_gpt", like_config(width, heads, args.layers or 4))):
+        beside = args.beside or "mqa_gpt"
+        beside_cfg = (DESIGNS[beside][1] if beside in DESIGNS else like_config)(width, heads, args.layers or 4)
+        for label, cfg in ((args.design, design_config(width, heads, args.layers or 4)), (beside, beside_cfg)):
             mc = ModelConfig.from_dict(cfg)
             page = 64
             pages = batch * (ctx // page + 4) + Tp // page + 8
@@ -522,7 +551,7 @@ def run_design(args, pk):
             for _ in range(3):
                 prefill_once()
             p_ms = timed(prefill_once, 5) / 5
-            window = design_window if label == args.design else 0
+            window = DESIGNS[label][2] if label in DESIGNS else 0
             saved_cap, eng.stepper.capture_repeated = eng.stepper.capture_repeated, False     # the recorded step runs eagerly
             p_ops = time_ops(eng, prefill_once, pk, [(Tp, Tp)], window)
             eng.stepper.capture_repeated = saved_cap
@@ -546,11 +575,11 @@ def run_design(args, pk):
             report[f"{label}_{width}"] = {
                 "prefill_tokens_per_s": round(Tp / (p_ms / 1e3)), "prefill_ms": round(p_ms, 3),
                 "decode_tokens_per_s": round(batch * K / (ms / 1e3)), "decode_ms_per_step": round(ms / K, 4),
-                "decode_launches_per_step": launches // K, "layers": len(mc.layers) if label == args.design else mc.num_layers,
+                "decode_launches_per_step": launches // K, "layers": len(mc.layers) if label in DESIGNS else mc.num_layers,
                 "prefill_ops": p_ops, "decode_ops": d_ops}
             del eng
             torch.cuda.empty_cache()
-    print(json.dumps({"design": DESIGNS[args.design][0], "beside": "mqa_gpt", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+    print(json.dumps({"design": DESIGNS[args.design][0], "beside": args.beside or "mqa_gpt", "dtype": "bf16", "data": "synthetic token ids, random-init weights",
                       "prefill_tokens": Tp, "decode_batch": batch, "decode_context": ctx, "steps": K, "warmup": W,
                       "peaks": pk, "sizes": report}))
     return 0
@@ -558,7 +587,8 @@ def run_design(args, pk):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=("munevik", "mizupel", "mokalorn"), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
+    ap.add_argument("--design", default=None, choices=("munevik", "mizupel", "mokalorn", "dabilorn"), help="prefill and decode of this design at a few sizes beside the closest existing model, with per-operation times")
+    ap.add_argument("--beside", default=None, choices=("mqa_gpt", "munevik", "mizupel", "mokalorn", "dabilorn"), help="with --design: the model it is timed beside (default: the multi-query GPT)")
     ap.add_argument("--sizes", default=None, help="with --design: comma-separated model widths (multiples of 128)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
