@@ -307,6 +307,37 @@ def test_sigmoid_attention_at_tensor_core_sizes(ops, dtype, heads, kv_heads, dim
         assert rel(got, exp) < (3e-5 if dtype == "float32" else 3e-2), cuts[:3]
 
 
+@pytest.mark.parametrize("chunk", [None, 200, 64])
+@pytest.mark.parametrize("heads,kv_heads,dim", [(8, 1, 128), (16, 2, 64), (4, 4, 128)])
+def test_sigmoid_attention_on_the_tcgen05_kernels(ops, heads, kv_heads, dim, chunk):
+    """Pages of 64 keys and head sizes of 64 and 128 in bfloat16: prompt portions of several hundred rows take the tcgen05
+    kernels (one and two query tiles per CTA), decoded tokens behind a long cache take the one-tile kernel with the key range
+    cut into pieces, some of which hold no visible key of a chunked row."""
+    L = attention_layer(chunk=chunk, rot={"base": 1e4, "dims": 32}, heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5)
+    part, w = part_with_weights("mixer", _mixer(L, "a", 96, 1e-6), "bfloat16", ops, 21, scales={"q.norm": 0.4, "k.norm": 0.4, "pb": 1.0})
+    S, page = 1100, 64
+    x = torch.randn(S, 96, generator=torch.Generator().manual_seed(22)).to(torch.bfloat16)
+    exp = pd.attention(x.double(), w, "", L["mixer"], 1e-6)
+    table = (torch.randperm(18, generator=torch.Generator().manual_seed(23)) + 1).to(torch.int32).to(DEV)[None]
+    kernels = set()
+    plan = ops.attention_plan
+
+    def noting(*a, **k):
+        out = plan(*a, **k)
+        kernels.add(out[0] + ("+pieces" if out[1] > 1 else ""))
+        return out
+
+    ops.attention_plan = noting
+    try:
+        for cuts in ([S], [600, 500], [1068] + [1] * 32, [300, 40, 760]):
+            got = run_paged(part, ops, "bfloat16", x, cuts, page, table, 20).cpu().double()
+            err = (got - exp).abs().max(dim=-1).values / exp.abs().max(dim=-1).values.clamp_min(exp.abs().max() * 0.05)
+            assert err.max() < 3e-2, (cuts[:3], int(err.argmax()), err.max())
+    finally:
+        ops.attention_plan = plan
+    assert any(k.startswith("tc") for k in kernels), kernels
+
+
 def loud_key(x, key_at, gain=40.0):
     """Makes the token at ``key_at`` one that every later query notices: its input row is scaled up, which the norms undo for the
     key's size but not for its direction, and the value it brings is large."""

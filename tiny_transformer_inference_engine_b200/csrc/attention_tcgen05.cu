@@ -159,7 +159,17 @@ struct AttnTcParams {
     int q_rows;                                                  // rows of the query tile that are staged (a multiple of 32 that covers every request's rows)
     int num_splits, split_len;                                   // keys per CTA along grid y (a multiple of 128); 1: no split
     float* ws_o; float* ws_ml;                                   // partial results [row][split][D] and [row][split][2] (max in natural log, sum)
+    int sigmoid;                                                 // 1: a visible key weighs sigmoid(score + head_bias[head]); no maximum, no rescaling, no division
+    const float* head_bias;                                      // [Hq] or null
 };
+
+// 1 / (1 + 2^-x): the sigmoid of a score in units of log2 e; x = -inf (a masked key) gives 1 / (1 + inf) = 0
+__device__ __forceinline__ float sigmoid_ex2(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return r;
+}
 
 constexpr int NP = 4;                                            // softmax threads per query row
 constexpr int NTHREADS = 64 + NP * 128;
@@ -227,7 +237,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             const int tok = row / G, g = row - tok * G;
             const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
             p.ws_o[(grow * p.num_splits + split) * D + (e - r * D)] = 0.f;
-            if (e - r * D == 0) { p.ws_ml[(grow * p.num_splits + split) * 2] = -INFINITY; p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = 0.f; }
+            if (e - r * D == 0) {                                  // (sigmoid weights: an empty piece still counts as one of the pieces that add)
+                p.ws_ml[(grow * p.num_splits + split) * 2] = p.sigmoid ? 0.f : -INFINITY;
+                p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = p.sigmoid ? 1.0f / (float)p.num_splits : 0.f;
+            }
         }
         return;
     }
@@ -457,6 +470,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
         for (int i = 0; i < OC; ++i) o[i] = 0.f;
         float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        const float hb2 = (p.sigmoid && p.head_bias && valid) ? p.head_bias[kvh * G + g] * 1.4426950408889634f : 0.f;
         bool ok = true;
         for (int j = 0; j <= ntiles && ok; ++j) {
             if (j < ntiles) {
@@ -499,12 +513,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
                 for (int k = 0; k < NP; ++k) mx = fmaxf(mx, xch[j & 1][k][r]);
                 mx *= p.scale_log2;                                      // -inf stays -inf (the scale is positive)
-                const float m_new = fmaxf(m_run, mx);
+                const float m_new = p.sigmoid ? m_run : fmaxf(m_run, mx);       // (sigmoid weights: nothing is ever rescaled)
                 const float msub = m_new == -INFINITY ? 0.f : m_new;
                 const float alpha = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
                 // probabilities, rounded to bfloat16 into the operand layout; their sum in float32
                 float ls4[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t packed[SC / 2];
+                if (p.sigmoid) {
+#pragma unroll
+                    for (int i = 0; i < SC; i += 2) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(sigmoid_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, hb2)),
+                                                                 sigmoid_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, hb2)));
+                        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                } else {
 #pragma unroll
                 for (int i = 0; i < SC; i += 2) {
                     const float p0 = ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -msub));
@@ -512,6 +534,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     ls4[(i >> 1) & 3] += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                }
                 }
                 // P over the scores of this tile: every thread of the row has its scores in registers (the exchange
                 // above came after the loads), so the columns can be overwritten; 32 keys = 16 packed columns
@@ -554,6 +577,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             ok = mbar_wait(BAR(XL), 0, 12);
 #pragma unroll
             for (int k = 0; k < NP; ++k) l_tot += xch[ntiles & 1][k][r];
+        }
+        if (p.sigmoid) {                                                 // the pieces of a cut key range simply add: (maximum 0, sum 1 / pieces)
+            l_tot = p.num_splits > 1 ? 1.0f / (float)p.num_splits : 1.f;
+            m_run = 0.f;
         }
         if (ok && valid && p.num_splits > 1) {
             const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
@@ -692,7 +719,10 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             const int tok = row / G, g = row - tok * G;
             const size_t grow = (size_t)(q0 + tok) * p.Hq + kvh * G + g;
             p.ws_o[(grow * p.num_splits + split) * D + (e - r * D)] = 0.f;
-            if (e - r * D == 0) { p.ws_ml[(grow * p.num_splits + split) * 2] = -INFINITY; p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = 0.f; }
+            if (e - r * D == 0) {                                  // (sigmoid weights: an empty piece still counts as one of the pieces that add)
+                p.ws_ml[(grow * p.num_splits + split) * 2] = p.sigmoid ? 0.f : -INFINITY;
+                p.ws_ml[(grow * p.num_splits + split) * 2 + 1] = p.sigmoid ? 1.0f / (float)p.num_splits : 0.f;
+            }
         }
         return;
     }
@@ -744,6 +774,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             const uint32_t s_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + S_COL + (uint32_t)t * 128;
             const float sl2 = p.scale_log2;
             float m_run = -INFINITY, l_run = 0.f;
+            const float hb2 = (p.sigmoid && p.head_bias && valid) ? p.head_bias[kvh * G + (row - tok * G)] * 1.4426950408889634f : 0.f;
             bool ok = true;
             for (int j = 0; j < nsteps; ++j) {
                 const int b = j & 1;
@@ -781,7 +812,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 // The maximum in use moves only when it has grown by more than the threshold (or was -inf): then the
                 // row of O is scaled by alpha before this step's product is added.
                 const float m_cand = fmaxf(m_run, mx);
-                const bool up = (m_cand - m_run) > RESCALE_LOG2;             // false for -inf - -inf (NaN)
+                const bool up = !p.sigmoid && (m_cand - m_run) > RESCALE_LOG2;   // false for -inf - -inf (NaN); sigmoid weights: never
                 const float alpha = up ? ex2(m_run - m_cand) : 1.f;
                 m_run = up ? m_cand : m_run;
                 alpha_s[b][t][r] = j > 0 ? alpha : 1.f;                      // nothing to scale before the first product
@@ -792,6 +823,15 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < BNK / 32; ++c) {
                     uint32_t packed[16];
+                    if (p.sigmoid) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float x0, x1;
+                            fma2(x0, x1, __uint_as_float(sv[c * 32 + i]), __uint_as_float(sv[c * 32 + i + 1]), sl2, hb2);
+                            __nv_bfloat162 h = __floats2bfloat162_rn(sigmoid_ex2(x0), sigmoid_ex2(x1));
+                            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    } else {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         float x0, x1;
@@ -801,6 +841,7 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
                     }
+                    }
                     tmem_st16(s_addr + c * 16, packed);                  // P over the scores: 32 keys = 16 packed columns
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -808,9 +849,9 @@ attn_tc_pp_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 mbar_arrive(BAR(PP_PF + 2 * t + b));                     // P is in tensor memory
                 l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
             }
-            if (ok) {
-                lsum_s[t][r] = l_run;
-                mrun_s[t][r] = m_run;
+            if (ok) {                                                    // (sigmoid weights: the pieces of a cut key range simply add)
+                lsum_s[t][r] = p.sigmoid ? (p.num_splits > 1 ? 1.0f / (float)p.num_splits : 1.f) : l_run;
+                mrun_s[t][r] = p.sigmoid ? 0.f : m_run;
                 mbar_arrive(BAR(PP_LF + t));
             }
         }
@@ -1150,12 +1191,30 @@ extern "C" int ttie_attn_tc_supported(int D, int page_size) {
 // kernel for prompt portions: a CTA owns 256 rows as two tiles taken in turns (128 rows as one tile at head size 256).
 // num_splits > 1: the key range is cut into pieces of split_len keys (a multiple of 128) over grid y; the partial
 // results go to `scratch` (ttie_attn_scratch_floats) and a merge kernel writes `out`.
+// weights 0: softmax; 1: sigmoid(score + head_bias[head]) per visible key (head_bias float32 [Hq] or null)
+extern "C" int ttie_paged_attention_tc_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                               int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
+                                               const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                               int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                               float* scratch, int two_tiles, int weights, const float* head_bias, void* stream);
+
 extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                        int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
                                        const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
                                        int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len, float* scratch,
                                        int two_tiles, void* stream) {
+    return ttie_paged_attention_tc_weights(q, q_stride, k_pages, v_pages, num_pages, block_table, table_width, page_size, qsl, seq_lens, out, T,
+                                           num_seqs, Hq, Hkv, D, max_q_len, scale, softcap, window, chunk, num_splits, split_len, scratch,
+                                           two_tiles, 0, nullptr, stream);
+}
+
+extern "C" int ttie_paged_attention_tc_weights(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                               int num_pages, const int* block_table, int table_width, int page_size, const int* qsl,
+                                               const int* seq_lens, void* out, int T, int num_seqs, int Hq, int Hkv, int D,
+                                               int max_q_len, float scale, float softcap, int window, int chunk, int num_splits, int split_len,
+                                               float* scratch, int two_tiles, int weights, const float* head_bias, void* stream) {
     if (T <= 0 || num_seqs <= 0) return 0;
+    if (weights != 0 && weights != 1) TTIE_FAIL("attention_tc: unknown kind of weights %d", weights);
     if (!ttie_attn_tc_supported(D, page_size)) TTIE_FAIL("attention_tc: head size %d with pages of %d keys is not supported", D, page_size);
     if (Hkv <= 0 || Hq % Hkv) TTIE_FAIL("attention_tc: %d heads are not a multiple of %d kv heads", Hq, Hkv);
     if (q_stride % 8 || ((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out | (uintptr_t)scratch) & 15)
@@ -1178,6 +1237,7 @@ extern "C" int ttie_paged_attention_tc(const void* q, long long q_stride, const 
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
     p.row_tiles = ceil_div(max_q_len * (Hq / Hkv), two_tiles && D <= 128 ? 2 * BM : BM);
     p.num_splits = num_splits; p.split_len = split_len;
+    p.sigmoid = weights; p.head_bias = head_bias;
     p.ws_o = scratch; p.ws_ml = scratch ? scratch + (size_t)T * Hq * num_splits * D : nullptr;
     if ((long long)num_seqs * Hkv * p.row_tiles > 2147483647LL) TTIE_FAIL("attention_tc: grid too large");
     cudaStream_t s = (cudaStream_t)stream;

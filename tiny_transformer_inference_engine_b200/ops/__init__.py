@@ -60,6 +60,9 @@ _SIGNATURES = {
     "ttie_paged_attention_tc": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int,
                                 _c_void],
+    "ttie_paged_attention_tc_weights": [_c_void, _c_ll, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void, _c_void, _c_void,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int,
+                                        _c_int, _c_void, _c_void],
     "ttie_gemm_tc": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_gemm_tc_pair": [_c_void, _c_ll, _c_void, _c_ll, _c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_scale_add_layernorm": [_c_void, _c_void, _c_int, _c_void, _c_int, _c_ll, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
@@ -606,14 +609,14 @@ class CudaOps:
         self.launches += 1
 
     def attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size=None,
-                       tile_loop_only=False):
+                       no_cluster_form=False):
         """Which attention kernel runs and how the key range is split: (kernel, num_splits,
         split_len).  bfloat16 with a head size that is a multiple of 16 up to 128, or 256, runs
         on tensor cores; everything else runs the general float32-arithmetic kernel.  The key
         range is split only when the query rows alone cannot fill the GPU.  Every layer of a step
-        asks the same question, so the answers are kept.  ``tile_loop_only``: the choice is between the ``mma.sync`` tile loop
-        and the general kernel (weights that only those two compute)."""
-        key = (dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, bool(tile_loop_only))
+        asks the same question, so the answers are kept.  ``no_cluster_form``: the thread-block-cluster decode form is left out
+        of the choice (sigmoid weights, which every other kernel computes)."""
+        key = (dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, bool(no_cluster_form))
         plan = self._plans.get(key)
         if plan is None:
             if len(self._plans) >= 4096:
@@ -621,11 +624,9 @@ class CudaOps:
             plan = self._plans[key] = self._attention_plan(*key)
         return plan
 
-    def _attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, tile_loop_only=False):
+    def _attention_plan(self, dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, no_cluster_form=False):
         G = num_heads // num_kv_heads
         rows = max_q_len * G
-        if tile_loop_only:
-            page_size = None                                         # (no tcgen05 kernel, whose page sizes would matter)
         if (dtype == torch.bfloat16 and page_size is not None and head_dim > 128
                 and self.lib.ttie_attn_tc_supported(head_dim, page_size)):
             return self._tc_wide_plan(num_seqs, num_kv_heads, rows, max_kv_len, max_q_len)
@@ -650,10 +651,10 @@ class CudaOps:
             # per kv head, head size 64 or 128) - since it stages only the rows in use and sets itself up while its
             # predecessor finishes it is ahead of the decode form at every context (8 requests x 32 heads: 7.1 against
             # 10.7 us at 100 keys, 8.8 against 10.6 at 1,024, 9.6 against 10.7 at 2,048) -, else the decode form
-            plan = None if tile_loop_only else self._tc_split_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
+            plan = self._tc_split_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size)
             if plan is not None:
                 return plan
-            plan = None if tile_loop_only else self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
+            plan = None if no_cluster_form else self._cluster_plan(num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len)
             if plan is not None:
                 return plan
             kernel, tile_rows, unit, min_len = "mma", self.lib.ttie_attn_mma_tile_rows(max_q_len, num_heads, num_kv_heads), 64, 128
@@ -824,7 +825,7 @@ class CudaOps:
         chunk of ``chunk`` positions up to p, chunks counted from position 0 of the sequence.  ``softcap`` > 0: a score s
         (scale applied) becomes softcap * tanh(s / softcap) before mask and softmax.  ``weights`` "sigmoid": a visible key
         weighs sigmoid(score + head_bias[head]) (``head_bias`` float32 [num_heads] or None) and nothing is normalised over the
-        keys; such steps run the general kernel or the ``mma.sync`` tile loop."""
+        keys; every kernel but the thread-block-cluster decode form computes them."""
         if weights not in ("softmax", "sigmoid"):
             raise KernelError(f"paged_attention: unknown kind of weights {weights!r}")
         sig = weights == "sigmoid"
@@ -834,18 +835,18 @@ class CudaOps:
         if max_kv_len > block_table.shape[1] * page_size:
             raise KernelError(f"paged_attention: a block table of {block_table.shape[1]} pages of {page_size} keys cannot cover {max_kv_len} keys")
         kernel, num_splits, split_len = plan if plan is not None else self.attention_plan(
-            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, None if sig else page_size, sig)
-        if sig and kernel not in ("mma", "simt"):
+            qkv.dtype, num_seqs, num_heads, num_kv_heads, head_dim, max_q_len, max_kv_len, page_size, sig)
+        if sig and kernel not in ("mma", "simt", "tc", "tcpp"):
             raise KernelError(f"paged_attention: sigmoid weights have no {kernel!r} kernel")
         if kernel in ("tc", "tcpp"):
             scratch = None
             if num_splits > 1:
                 scratch = torch.empty((T * num_heads * num_splits * (head_dim + 2),), dtype=torch.float32, device=qkv.device)
-            self._check(self.lib.ttie_paged_attention_tc(
+            self._check(self.lib.ttie_paged_attention_tc_weights(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(block_table),
                 block_table.shape[1], page_size, _ptr(query_start_loc), _ptr(seq_lens), _ptr(out), T, num_seqs, num_heads,
                 num_kv_heads, head_dim, max_q_len, float(scale), float(softcap or 0.0), int(window), int(chunk), num_splits, split_len, _ptr(scratch),
-                1 if kernel == "tcpp" else 0, self._stream(qkv)), "paged_attention_tc")
+                1 if kernel == "tcpp" else 0, 1 if sig else 0, _ptr(head_bias), self._stream(qkv)), "paged_attention_tc")
             self.launches += 2 if num_splits > 1 else 1
             return
         form = {"mma": 0, "mma_c2": 2, "mma_c4": 4}.get(kernel)
