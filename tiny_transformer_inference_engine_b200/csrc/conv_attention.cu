@@ -288,35 +288,67 @@ __global__ void __launch_bounds__(128) proj_row_rms_kernel(const T* __restrict__
     }
 }
 
-// one thread per (token, four channels); x [T, C] 32-bit, w [taps][C], tail [slots + 1][taps - 1][C]
-template <typename TO, int V>
+// one thread per (tile of CONV_TOKENS tokens, four channels); x [T, C] 32-bit, w [taps][C], tail [slots + 1][taps - 1][C].  The tokens of a
+// tile are independent: their look-ups and loads are all asked for before the first sum is needed (prompt portions: tiles of 8
+// tokens; steps of a few tokens: one token per thread, so that every token has threads of its own).
+template <typename TO, int V, int CONV_TOKENS>
 __global__ void __launch_bounds__(128) stream_conv_kernel(const float* __restrict__ x, int T_, int C, int taps, const float* __restrict__ w,
                                                           const float* __restrict__ tail, int tail_rows, const int* __restrict__ token_seq,
                                                           const int* __restrict__ qsl, const int* __restrict__ slot_ids, TO* __restrict__ out) {
     TTIE_PDL_ENTRY();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (c >= C) return;
-    for (int t = blockIdx.y; t < T_; t += gridDim.y) {
-        const int s = token_seq[t];
-        const int j = t - qsl[s];                                   // index among the request's tokens of this step
-        const float* mine = taps > 1 ? tail + (size_t)slot_row_(slot_ids[s], tail_rows) * (taps - 1) * C : nullptr;
-        float acc[V];
+    for (int t0 = blockIdx.y * CONV_TOKENS; t0 < T_; t0 += gridDim.y * CONV_TOKENS) {
+        int js[CONV_TOKENS];
+        const float* mine[CONV_TOKENS];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int m = 0; m < CONV_TOKENS; ++m) {
+            const int t = min(t0 + m, T_ - 1);
+            const int s = token_seq[t];
+            js[m] = t - qsl[s];                                     // index among the request's tokens of this step
+            mine[m] = taps > 1 ? tail + (size_t)slot_row_(slot_ids[s], tail_rows) * (taps - 1) * C : nullptr;
+        }
+        float acc[CONV_TOKENS][V];
+#pragma unroll
+        for (int m = 0; m < CONV_TOKENS; ++m)
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[m][i] = 0.f;
         for (int k = 0; k < taps; ++k) {
-            const int src = j - (taps - 1) + k;
-            const float* u = src >= 0 ? x + (size_t)(t - j + src) * C + c : mine + (size_t)(taps - 1 + src) * C + c;
             const float* wk = w + (size_t)k * C + c;
-            if (V == 4) {
-                const float4 uv = *reinterpret_cast<const float4*>(u), wv = __ldg(reinterpret_cast<const float4*>(wk));
-                acc[0] = fmaf(wv.x, uv.x, acc[0]); acc[1 % V] = fmaf(wv.y, uv.y, acc[1 % V]);
-                acc[2 % V] = fmaf(wv.z, uv.z, acc[2 % V]); acc[3 % V] = fmaf(wv.w, uv.w, acc[3 % V]);
-            } else {
-                acc[0] = fmaf(wk[0], u[0], acc[0]);
+            float wv[V];
+            if (V == 4) { const float4 v4 = __ldg(reinterpret_cast<const float4*>(wk)); wv[0] = v4.x; wv[1 % V] = v4.y; wv[2 % V] = v4.z; wv[3 % V] = v4.w; }
+            else wv[0] = wk[0];
+#pragma unroll
+            for (int m = 0; m < CONV_TOKENS; ++m) {
+                const int t = min(t0 + m, T_ - 1);
+                const int src = js[m] - (taps - 1) + k;
+                const float* u = src >= 0 ? x + (size_t)(t - js[m] + src) * C + c : mine[m] + (size_t)(taps - 1 + src) * C + c;
+                if (V == 4) {
+                    const float4 uv = *reinterpret_cast<const float4*>(u);
+                    acc[m][0] = fmaf(wv[0], uv.x, acc[m][0]); acc[m][1 % V] = fmaf(wv[1 % V], uv.y, acc[m][1 % V]);
+                    acc[m][2 % V] = fmaf(wv[2 % V], uv.z, acc[m][2 % V]); acc[m][3 % V] = fmaf(wv[3 % V], uv.w, acc[m][3 % V]);
+                } else {
+                    acc[m][0] = fmaf(wv[0], u[0], acc[m][0]);
+                }
             }
         }
 #pragma unroll
-        for (int i = 0; i < V; ++i) out[(size_t)t * C + c + i] = from_f32<TO>(acc[i]);
+        for (int m = 0; m < CONV_TOKENS; ++m) {
+            if (t0 + m >= T_) break;
+            TO* o = out + (size_t)(t0 + m) * C + c;
+            if (V == 4 && sizeof(TO) == 2) {                          // four bfloat16 values: one 8-byte store (C and c are multiples of 4)
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[m][0], acc[m][1 % V]), hi = __floats2bfloat162_rn(acc[m][2 % V], acc[m][3 % V]);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const unsigned*>(&lo);
+                packed.y = *reinterpret_cast<const unsigned*>(&hi);
+                *reinterpret_cast<uint2*>(o) = packed;
+            } else if (V == 4) {
+                *reinterpret_cast<float4*>(o) = make_float4(acc[m][0], acc[m][1 % V], acc[m][2 % V], acc[m][3 % V]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) o[i] = from_f32<TO>(acc[m][i]);
+            }
+        }
     }
 }
 
@@ -438,9 +470,12 @@ extern "C" int ttie_stream_conv(const float* x, int T, int C, int taps, const fl
     if (T <= 0) return 0;
     if (taps < 1 || (taps > 1 && !tail)) TTIE_FAIL("stream_conv: %d taps need state rows", taps);
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = C % 4 == 0 && !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)tail) & 15);
-    const dim3 grid(ceil_div(vec ? C / 4 : C, 128), T < 65535 ? T : 65535);
-#define SC(TO, V) TTIE_LAUNCH((stream_conv_kernel<TO, V>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out)
+    const bool vec = C % 4 == 0 && !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)tail | (uintptr_t)out) & 15);
+    const bool tiled = T >= 64;
+    const int tiles = ceil_div(T, tiled ? 8 : 1);
+    const dim3 grid(ceil_div(vec ? C / 4 : C, 128), tiles < 65535 ? tiles : 65535);
+#define SC(TO, V) do { if (tiled) TTIE_LAUNCH((stream_conv_kernel<TO, V, 8>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out); \
+                       else TTIE_LAUNCH((stream_conv_kernel<TO, V, 1>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out); } while (0)
     if (out_dtype == kF32) { if (vec) SC(float, 4); else SC(float, 1); }
     else if (out_dtype == kBF16) { if (vec) SC(__nv_bfloat16, 4); else SC(__nv_bfloat16, 1); }
     else TTIE_FAIL("stream_conv: unknown dtype %d", out_dtype);
