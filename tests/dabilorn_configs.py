@@ -68,7 +68,7 @@ DAB_B = model(97, 50, 3e-4, 1, [
 # meets, five taps, a latent row of 128 values
 DAB_C = model(120, 128, 1e-6, 5, [
     layer("attention", attn(8, 2, 64, 64, 0.125, chunk=32, rot={"base": 1000.0, "dims": 16}), moe(8, 2, 64, shared=32)),
-    layer("latent_attention", latent(4, 32, 32, 32, 96, 64, 0.12, base=1e5, scaling=yarn(2.0, 128, 16.0, 2.0)), moe(8, 2, 64, shared=32)),
+    layer("latent_attention", latent(4, 32, 24, 32, 104, 64, 0.12, base=1e5, scaling=yarn(2.0, 128, 16.0, 2.0)), moe(8, 2, 64, shared=32)),
     layer("wkv", wkv(2, 64, 16), moe(6, 4, 32)),
     layer("attention", attn(2, 2, 128, 128, 0.09, chunk=70, rot={"base": 500.0, "dims": 128}))])
 

@@ -89,7 +89,7 @@ def test_pages_of_past_chunks_go_back():
 
 @pytest.mark.parametrize("rot", [
     {"base": 50.0, "dims": 8, "scaling": yarn(4.0, 64, 8.0, 1.0)},
-    {"base": 1e6, "dims": 16, "scaling": yarn(2.0, 2048, 32.0, 1.0)},          # the ramp ends inside the pairs
+    {"base": 5e5, "dims": 12, "scaling": yarn(3.0, 1024, 16.0, 2.0)},          # the ramp ends inside the pairs
     {"base": 10.0, "dims": 6, "scaling": yarn(8.0, 32, 4.0, 0.5)},
     {"base": 1e4, "dims": 64, "scaling": yarn(16.0, 4096, 32.0, 1.0)},
     {"base": 1e4, "dims": 4, "scaling": yarn(3.0, 8, 1.0, 1.0)},               # lo == hi: the 0.001 floor decides

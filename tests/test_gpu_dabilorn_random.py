@@ -24,13 +24,13 @@ def draw(seed):
             heads = kv * r.choice([1, 2, 4])
             dim = r.choice([4, 8, 10, 16, 24, 32, 64, 128])
             scale = r.choice([1.0, 0.5, 2.0]) * dim ** -0.5
-            rot = None if r.random() < 0.2 else {"base": r.choice([20.0, 1e3, 1e4, 2.5e5]), "dims": r.choice([d for d in (2, 4, 8, 16, dim) if d <= dim])}
-            chunk = None if r.random() < 0.15 else r.choice([1, 2, 5, 8, 13, 16, 24, 33, 64, 96, 300])
+            rot = None if r.random() < 0.2 else {"base": r.choice([20.0, 1e3, 1e4, 3e5]), "dims": r.choice([d for d in (2, 4, 8, 16, dim) if d <= dim])}
+            chunk = None if r.random() < 0.15 else r.choice([1, 2, 5, 8, 13, 16, 24, 33, 64, 80, 300])
             mixer = attn(heads, kv, dim, r.choice([4, 8, 12, 16, 32, 64, dim]), scale, chunk=chunk, rot=rot)
         else:
             dim, rot_dim = r.choice([4, 8, 12, 16, 32, 64]), r.choice([0, 2, 4, 8, 16, 32])
             scaling = None if r.random() < 0.4 else yarn(r.choice([2.0, 4.0, 8.0]), r.choice([16, 64, 256]), r.choice([4.0, 16.0, 32.0]), r.choice([0.5, 1.0, 2.0]))
-            mixer = latent(r.choice([1, 2, 3, 4, 6]), dim, rot_dim, r.choice([4, 8, 16, 20, 32, 64]), r.choice([8, 12, 16, 40, 64, 96]),
+            mixer = latent(r.choice([1, 2, 3, 4, 6]), dim, rot_dim, r.choice([4, 8, 16, 20, 32, 64]), r.choice([8, 12, 16, 40, 64, 104]),
                            r.choice([4, 8, 24, 48, 100]), r.choice([1.0, 0.5]) * (dim + rot_dim) ** -0.5, base=r.choice([10.0, 1e3, 1e4, 1e6]),
                            scaling=scaling)
         if r.random() < 0.2:
