@@ -530,8 +530,11 @@ def test_stream_convolution_and_its_state(ops, dtype, d, taps):
                 continue
             ctx = ctx_for(ops, DT[dtype], seqs, None, slots=[slots[i] for i in rows])
             resid = torch.cat([xs[i][done[i]:done[i] + k] for i, (_, k) in zip(rows, seqs)]).to(DEV)
-            h = ops.stream_conv(resid, conv_w, taps, state if taps > 1 else None, ctx.token_seq, ctx.query_start_loc, ctx.slot_ids, DT[dtype])
-            ops.conv_tail_update(resid, d, taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
+            fused = n == 1                                              # one token per request: the kernel advances the state rows itself
+            h = ops.stream_conv(resid, conv_w, taps, state if taps > 1 else None, ctx.token_seq, ctx.query_start_loc, ctx.slot_ids, DT[dtype],
+                                update_tail=fused)
+            if not fused:
+                ops.conv_tail_update(resid, d, taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
             at = 0
             for i, (_, k) in zip(rows, seqs):
                 outs[i].append(h[at:at + k].float()); at += k; done[i] += k

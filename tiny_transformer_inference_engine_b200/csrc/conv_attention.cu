@@ -293,14 +293,15 @@ __global__ void __launch_bounds__(128) proj_row_rms_kernel(const T* __restrict__
 // tokens; steps of a few tokens: one token per thread, so that every token has threads of its own).
 template <typename TO, int V, int CONV_TOKENS>
 __global__ void __launch_bounds__(128) stream_conv_kernel(const float* __restrict__ x, int T_, int C, int taps, const float* __restrict__ w,
-                                                          const float* __restrict__ tail, int tail_rows, const int* __restrict__ token_seq,
-                                                          const int* __restrict__ qsl, const int* __restrict__ slot_ids, TO* __restrict__ out) {
+                                                          float* tail, int tail_rows, const int* __restrict__ token_seq,
+                                                          const int* __restrict__ qsl, const int* __restrict__ slot_ids, TO* __restrict__ out,
+                                                          int update_tail) {
     TTIE_PDL_ENTRY();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (c >= C) return;
     for (int t0 = blockIdx.y * CONV_TOKENS; t0 < T_; t0 += gridDim.y * CONV_TOKENS) {
         int js[CONV_TOKENS];
-        const float* mine[CONV_TOKENS];
+        float* mine[CONV_TOKENS];
 #pragma unroll
         for (int m = 0; m < CONV_TOKENS; ++m) {
             const int t = min(t0 + m, T_ - 1);
@@ -323,12 +324,18 @@ __global__ void __launch_bounds__(128) stream_conv_kernel(const float* __restric
                 const int t = min(t0 + m, T_ - 1);
                 const int src = js[m] - (taps - 1) + k;
                 const float* u = src >= 0 ? x + (size_t)(t - js[m] + src) * C + c : mine[m] + (size_t)(taps - 1 + src) * C + c;
+                // update_tail (every request of the step brings one token, so this thread alone reads its request's state row for
+                // its channels): the row that tap k read moves one place up; the token's own row becomes the newest
+                float* up = (CONV_TOKENS == 1 && update_tail && k >= 1) ? mine[m] + (size_t)(k - 1) * C + c : nullptr;
                 if (V == 4) {
                     const float4 uv = *reinterpret_cast<const float4*>(u);
                     acc[m][0] = fmaf(wv[0], uv.x, acc[m][0]); acc[m][1 % V] = fmaf(wv[1 % V], uv.y, acc[m][1 % V]);
                     acc[m][2 % V] = fmaf(wv[2 % V], uv.z, acc[m][2 % V]); acc[m][3 % V] = fmaf(wv[3 % V], uv.w, acc[m][3 % V]);
+                    if (up) *reinterpret_cast<float4*>(up) = uv;
                 } else {
-                    acc[m][0] = fmaf(wv[0], u[0], acc[m][0]);
+                    const float u0 = u[0];
+                    acc[m][0] = fmaf(wv[0], u0, acc[m][0]);
+                    if (up) up[0] = u0;
                 }
             }
         }
@@ -465,17 +472,20 @@ extern "C" int ttie_proj_row_rms(const void* proj, long long ld, int T, int nq, 
     return 0;
 }
 
-extern "C" int ttie_stream_conv(const float* x, int T, int C, int taps, const float* w, const float* tail, int tail_rows,
-                                const int* token_seq, const int* qsl, const int* slot_ids, void* out, int out_dtype, void* stream) {
+// update_tail: also advance the state rows (only for a step in which every request brings exactly one token; any other step is
+// followed by conv_tail_update)
+extern "C" int ttie_stream_conv(const float* x, int T, int C, int taps, const float* w, float* tail, int tail_rows,
+                                const int* token_seq, const int* qsl, const int* slot_ids, void* out, int out_dtype, int update_tail,
+                                void* stream) {
     if (T <= 0) return 0;
     if (taps < 1 || (taps > 1 && !tail)) TTIE_FAIL("stream_conv: %d taps need state rows", taps);
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = C % 4 == 0 && !(((uintptr_t)x | (uintptr_t)w | (uintptr_t)tail | (uintptr_t)out) & 15);
-    const bool tiled = T >= 64;
+    const bool tiled = T >= 64 && !update_tail;
     const int tiles = ceil_div(T, tiled ? 8 : 1);
     const dim3 grid(ceil_div(vec ? C / 4 : C, 128), tiles < 65535 ? tiles : 65535);
-#define SC(TO, V) do { if (tiled) TTIE_LAUNCH((stream_conv_kernel<TO, V, 8>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out); \
-                       else TTIE_LAUNCH((stream_conv_kernel<TO, V, 1>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out); } while (0)
+#define SC(TO, V) do { if (tiled) TTIE_LAUNCH((stream_conv_kernel<TO, V, 8>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out, 0); \
+                       else TTIE_LAUNCH((stream_conv_kernel<TO, V, 1>), grid, 128, 0, s, x, T, C, taps, w, tail, tail_rows, token_seq, qsl, slot_ids, (TO*)out, update_tail); } while (0)
     if (out_dtype == kF32) { if (vec) SC(float, 4); else SC(float, 1); }
     else if (out_dtype == kBF16) { if (vec) SC(__nv_bfloat16, 4); else SC(__nv_bfloat16, 1); }
     else TTIE_FAIL("stream_conv: unknown dtype %d", out_dtype);

@@ -96,7 +96,7 @@ _SIGNATURES = {
                                  _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_float, _c_void, _c_int, _c_float, _c_int,
                                  _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ttie_proj_row_rms": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_float, _c_void, _c_int, _c_void],
-    "ttie_stream_conv": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void],
+    "ttie_stream_conv": [_c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ttie_conv_tail_update": [_c_void, _c_ll, _c_int, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ttie_gate_head_rows": [_c_void, _c_void, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ttie_token_shift_mix": [_c_void, _c_ll, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int,
@@ -942,15 +942,16 @@ class CudaOps:
         return out
 
     # ---- a causal convolution over time on the rows of the 32-bit residual stream
-    def stream_conv(self, resid, conv_w, taps, tail, token_seq, query_start_loc, slot_ids, dtype):
+    def stream_conv(self, resid, conv_w, taps, tail, token_seq, query_start_loc, slot_ids, dtype, update_tail=False):
         """h[t] = sum_k conv_w[k] * x_(t - taps + 1 + k) per channel over the stream rows ``resid`` float32 [T, d]; ``conv_w``
         float32 tap-major [taps, d]; rows before the step come from ``tail`` float32 [slots + 1, taps - 1, d] (None with one
-        tap).  Returns h [T, d] in ``dtype``.  ``conv_tail_update`` (given ``resid``) advances the state rows afterwards."""
+        tap).  Returns h [T, d] in ``dtype``.  ``conv_tail_update`` (given ``resid``) advances the state rows afterwards -
+        or this call does, with ``update_tail``, which is only right for a step in which every request brings one token."""
         T, d = resid.shape
         out = torch.empty((T, d), dtype=dtype, device=resid.device)
         self._check(self.lib.ttie_stream_conv(_ptr(resid), T, d, int(taps), _ptr(conv_w), _ptr(tail), 0 if tail is None else tail.shape[0],
                                               _ptr(token_seq), _ptr(query_start_loc), _ptr(slot_ids), _ptr(out), _DT[dtype],
-                                              self._stream(resid)), "stream_conv")
+                                              1 if (update_tail and tail is not None) else 0, self._stream(resid)), "stream_conv")
         self.launches += 1
         return out
 

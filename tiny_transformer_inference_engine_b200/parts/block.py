@@ -87,7 +87,8 @@ class SublayerNormBlock(Block):
     every channel, ``conv(x)_t = sum_j w[:, j] * x_(t - taps + 1 + j)`` with zeros before the sequence's start (tensor ``name``
     [dim, taps]; tap ``taps - 1`` multiplies the current token).  The ``x`` itself is one more on the last tap, added in 32-bit
     when the tensor is loaded; the kernel reads the 32-bit stream, and the last ``taps - 1`` stream rows of a request are kept
-    in a state row of this block (the first of its cache needs)."""
+    in a state row of this block (the first of its cache needs), advanced by the convolution kernel itself in steps of one token
+    per request and by a second kernel otherwise."""
 
     def __init__(self, prefix: str, dim: int, mixer: PartSpec, mixer_norm: PartSpec, ffn: PartSpec = None, ffn_norm: PartSpec = None,
                  input_conv: Optional[dict] = None):
@@ -130,8 +131,10 @@ class SublayerNormBlock(Block):
         if self.conv_name is not None:
             tail = caches.pop(0) if self.taps > 1 else None
             state = None if tail is None else tail.state
-            h = ops.stream_conv(resid, self.conv_w, self.taps, state, ctx.token_seq, ctx.query_start_loc, ctx.slot_ids, self.dtype)
-            if tail is not None and tail.writable:
+            decode = ctx.max_q_len == 1 and tail is not None and tail.writable      # one token per request: the same kernel advances the state rows
+            h = ops.stream_conv(resid, self.conv_w, self.taps, state, ctx.token_seq, ctx.query_start_loc, ctx.slot_ids, self.dtype,
+                                update_tail=decode)
+            if tail is not None and tail.writable and not decode:
                 ops.conv_tail_update(resid, self.dim, self.taps, state, ctx.query_start_loc, ctx.slot_ids, ctx.num_seqs)
         else:
             h = stream.x
