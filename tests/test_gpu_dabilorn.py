@@ -31,16 +31,16 @@ def ops():
     return get_ops(DEV)
 
 
-def weights_for(cfg, seed, store="float32"):
+def weights_for(cfg, seed, store="float32", sharp=True):
     """Random weights large enough that every mechanism matters: peaked attention, head biases and gates away from zero, layer
     scales and convolution taps of a size, router logits of a few units (the sub-layers read the stream itself, whose size
     grows from layer to layer: the router's rows are kept small so that the scores stay away from 1 and from each other)."""
     w = random_tensors(ModelConfig.from_dict(cfg), seed, std=0.08, perturb_norms=True, store_dtype=store)
     g = torch.Generator().manual_seed(seed + 1)
     for k in w:
-        if k.endswith((".mix.q", ".mix.k", ".mix.uq", ".mix.dkv")):
+        if sharp and k.endswith((".mix.q", ".mix.k", ".mix.uq", ".mix.dkv")):
             w[k] = w[k] * 3.0
-        if k.endswith(".up"):
+        if sharp and k.endswith(".up"):
             w[k] = w[k] * 4.0
         if k.endswith(".mlp.router"):
             w[k] = w[k] * (0.6 / (w[k].float().std() * cfg["width"] ** 0.5))
@@ -66,20 +66,21 @@ def expected_for(cfg, w, reqs, dtype):
     return {rid: pd.forward(cfg, ww, toks) for rid, toks in reqs.items()}
 
 
-def check(got, exp, dtype, tail16=0.15):
+def check(got, exp, dtype, tail16=0.15, worst32=1e-4):
     """32-bit: every place within 1e-4 of the row's largest logit.  bfloat16: these models are narrow and their weights are
     scaled up so that gates and routers bite; the sub-layers read the stream itself (nothing norms their input), an expert
     squares what it activates (a relative error doubles there) and the sigmoid weights of a chunk add up without a
     normalisation, so rounding alone moves a typical row by 2 to 4 % and a router's choice between two close experts, flipped
     by the rounding, moves one by tens of percent; the run is held to the typical error (every mechanism alone is held to
-    its largest error in both dtypes below).  ``tail16``: what nine rows in ten stay below in bfloat16."""
+    its largest error in both dtypes below).  ``tail16``: what nine rows in ten stay below in bfloat16; ``worst32``: the bound on
+    the worst row in 32-bit."""
     errs = []
     for (rid, pos), row in got.items():
         ref = exp[rid][pos]
         errs.append((((row.double() - ref).abs().max() / ref.abs().max()).item(), rid, pos))
     errs.sort(reverse=True)
     if dtype == "float32":
-        assert errs[0][0] < 1e-4, errs[:3]
+        assert errs[0][0] < worst32 and errs[len(errs) // 2][0] < 2e-5, errs[:3]
     else:
         n = len(errs)
         assert all(e[0] == e[0] for e in errs), "a NaN among the logits"
@@ -100,6 +101,31 @@ def test_schedules_against_plain_model(name, dtype):
         tokens = tu.max_live_tokens(steps, rounding=page)
         eng = engine_for(cfg, w, dtype, page=page, pages=tokens // page + 2)        # no slack: pages and slots are used again
         check(tu.run_steps(eng, steps), exp, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_wider_model_with_long_prompts_on_pages_of_16(dtype):
+    """Six layers at head sizes of 64 (the tensor-core kernels' sizes on pages of 16 keys), prompts of several hundred tokens, a
+    chunk that no page edge meets: whole, with a decoded tail, and mixed on a pool without slack.  The weights are the plain
+    random ones (not sharpened): over six layers and hundreds of positions a model of this design has tokens at which rounding is
+    magnified a hundredfold (the plain implementation run in 32-bit against itself in 64-bit shows the same rows: 7e-4 at one
+    token of 700), so the worst row in 32-bit is held to 2e-3 and the typical row to 2e-5."""
+    from dabilorn_configs import layer, moe, wkv, model
+    cfg = model(200, 256, 1e-5, 3, [
+        layer("latent_attention", latent(4, 64, 32, 64, 96, 80, 0.1, base=1e4, scaling=yarn(4.0, 256, 16.0, 1.0)), moe(6, 2, 64, shared=96)),
+        layer("attention", attn(8, 2, 64, 64, 0.125, chunk=80, rot={"base": 5e4, "dims": 32}), moe(6, 2, 64, shared=96)),
+        layer("wkv", wkv(4, 64, 12), moe(6, 2, 64, shared=96)),
+        layer("attention", attn(4, 4, 64, 64, 0.125, chunk=208, rot={"base": 5e4, "dims": 64}), moe(6, 2, 64, shared=96)),
+        layer("latent_attention", latent(4, 64, 32, 64, 96, 80, 0.1, base=1e4, scaling=yarn(4.0, 256, 16.0, 1.0)), moe(6, 2, 64, shared=96)),
+        layer("wkv", wkv(4, 64, 12))])
+    w = weights_for(cfg, 61, sharp=False)
+    reqs = requests(cfg, [700, 333, 41, 290], seed=6)
+    exp = expected_for(cfg, w, reqs, dtype)
+    for cut in (tu.whole, tu.prefill_then_decode, tu.mixed):
+        steps = cut(reqs)
+        tokens = tu.max_live_tokens(steps, rounding=16)
+        eng = engine_for(cfg, w, dtype, page=16, pages=tokens // 16 + 2, budget=1024)
+        check(tu.run_steps(eng, steps), exp, dtype, worst32=2e-3)
 
 
 def test_long_decode_past_chunks_and_pages():
@@ -307,18 +333,20 @@ def test_sigmoid_attention_at_tensor_core_sizes(ops, dtype, heads, kv_heads, dim
         assert rel(got, exp) < (3e-5 if dtype == "float32" else 3e-2), cuts[:3]
 
 
+@pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("chunk", [None, 200, 64])
 @pytest.mark.parametrize("heads,kv_heads,dim", [(8, 1, 128), (16, 2, 64), (4, 4, 128)])
-def test_sigmoid_attention_on_the_tcgen05_kernels(ops, heads, kv_heads, dim, chunk):
-    """Pages of 64 keys and head sizes of 64 and 128 in bfloat16: prompt portions of several hundred rows take the tcgen05
+def test_sigmoid_attention_on_the_tcgen05_kernels(ops, heads, kv_heads, dim, chunk, page):
+    """Pages of 16 and 64 keys and head sizes of 64 and 128 in bfloat16: prompt portions of several hundred rows take the tcgen05
     kernels (one and two query tiles per CTA), decoded tokens behind a long cache take the one-tile kernel with the key range
     cut into pieces, some of which hold no visible key of a chunked row."""
     L = attention_layer(chunk=chunk, rot={"base": 1e4, "dims": 32}, heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5)
     part, w = part_with_weights("mixer", _mixer(L, "a", 96, 1e-6), "bfloat16", ops, 21, scales={"q.norm": 0.4, "k.norm": 0.4, "pb": 1.0})
-    S, page = 1100, 64
+    S = 1100
     x = torch.randn(S, 96, generator=torch.Generator().manual_seed(22)).to(torch.bfloat16)
     exp = pd.attention(x.double(), w, "", L["mixer"], 1e-6)
-    table = (torch.randperm(18, generator=torch.Generator().manual_seed(23)) + 1).to(torch.int32).to(DEV)[None]
+    npages = -(-S // page) + 1
+    table = (torch.randperm(npages, generator=torch.Generator().manual_seed(23)) + 1).to(torch.int32).to(DEV)[None]
     kernels = set()
     plan = ops.attention_plan
 
@@ -330,7 +358,7 @@ def test_sigmoid_attention_on_the_tcgen05_kernels(ops, heads, kv_heads, dim, chu
     ops.attention_plan = noting
     try:
         for cuts in ([S], [600, 500], [1068] + [1] * 32, [300, 40, 760]):
-            got = run_paged(part, ops, "bfloat16", x, cuts, page, table, 20).cpu().double()
+            got = run_paged(part, ops, "bfloat16", x, cuts, page, table, npages + 2).cpu().double()
             err = (got - exp).abs().max(dim=-1).values / exp.abs().max(dim=-1).values.clamp_min(exp.abs().max() * 0.05)
             assert err.max() < 3e-2, (cuts[:3], int(err.argmax()), err.max())
     finally:
